@@ -25,7 +25,7 @@ class PagedView:
     """What an attention mixer gets: pools of its cache and the batch's block tables."""
 
     k_pool: torch.Tensor       # [pages, kv_heads, page_size, head_dim]
-    v_pool: torch.Tensor
+    v_pool: Optional[torch.Tensor]   # None for a cache of one pool (a latent from which keys and values are formed alike)
     block_table: torch.Tensor  # int32 [sequences, entries], -1 where no page
     page_size: int
     window: int
@@ -82,7 +82,7 @@ class CachePools:
                 geometry.append(GroupGeometry(num_pages, self.page_size, grp.spec.window))
                 shape = (n, num_pages, grp.spec.kv_heads, self.page_size, grp.spec.head_dim)
                 grp.k_pool = torch.zeros(shape, dtype=dtype, device=device)
-                grp.v_pool = torch.zeros(shape, dtype=dtype, device=device)
+                grp.v_pool = torch.zeros(shape, dtype=dtype, device=device) if grp.spec.values else None
             elif grp.spec.kind == "state":
                 sd = _STATE_DTYPES[grp.spec.state_dtype]
                 grp.state = torch.zeros((n, self.max_requests, *grp.spec.state_shape), dtype=sd, device=device)
@@ -114,12 +114,13 @@ class CachePools:
         g, i = self._where[cache_id]
         grp = self.groups[g]
         if grp.spec.kind == "paged":
-            return PagedView(grp.k_pool[i], grp.v_pool[i], batch.block_tables[grp.table_index], self.page_size,
+            return PagedView(grp.k_pool[i], grp.v_pool[i] if grp.v_pool is not None else None,
+                             batch.block_tables[grp.table_index], self.page_size,
                              grp.spec.window, read_only)
         return StateView(grp.state[i], batch.slots, batch.slots_host, read_only)
 
     def bytes_per_token(self) -> int:
         total = 0
         for grp in self.paged_groups:
-            total += 2 * len(grp.cache_ids) * grp.spec.kv_heads * grp.spec.head_dim * grp.k_pool.element_size()
+            total += (2 if grp.spec.values else 1) * len(grp.cache_ids) * grp.spec.kv_heads * grp.spec.head_dim * grp.k_pool.element_size()
         return total

@@ -12,7 +12,12 @@ constexpr int BM = 64, BN = 64, BK = 16;
 template <typename TA, typename TC>
 __global__ void __launch_bounds__(256) gemm_plain_kernel(const TA* __restrict__ A, const TA* __restrict__ W,
                                                          TC* __restrict__ C, int M, int N, int K, int lda,
-                                                         int ldw, int ldc) {
+                                                         int ldw, int ldc, long long batch_a, long long batch_w,
+                                                         long long batch_c) {
+    // blockIdx.z: one of several products of the same sizes whose operands lie batch_* elements apart (one per head)
+    A += (size_t)blockIdx.z * batch_a;
+    W += (size_t)blockIdx.z * batch_w;
+    C += (size_t)blockIdx.z * batch_c;
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -62,24 +67,33 @@ __global__ void __launch_bounds__(256) gemm_plain_kernel(const TA* __restrict__ 
 }  // namespace
 
 // in_dtype: type of A and W; out_dtype: type of C (float logits from bfloat16 operands are allowed).
-RMX_API int rmx_gemm_plain(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw,
-                           int ldc, int in_dtype, int out_dtype, void* stream) {
-    if (M == 0 || N == 0) return 0;
+// batch products of the same sizes, operand b at A + b * batch_a, W + b * batch_w, C + b * batch_c (elements): the
+// per-head products of a mixer whose heads have weights of their own, rows of all heads interleaved in A and C.
+RMX_API int rmx_gemm_plain_batched(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw,
+                                   int ldc, int batch, long long batch_a, long long batch_w, long long batch_c,
+                                   int in_dtype, int out_dtype, void* stream) {
+    if (M == 0 || N == 0 || batch == 0) return 0;
     RMX_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_plain: bad sizes M=%d N=%d K=%d", M, N, K);
     RMX_REQUIRE(lda >= K && ldw >= K && ldc >= N, "gemm_plain: leading dimensions too small");
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    RMX_REQUIRE(batch > 0 && batch <= 65535 && batch_a >= 0 && batch_w >= 0 && batch_c >= 0, "gemm_plain: bad batch");
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
     RMX_REQUIRE(grid.y <= 65535, "gemm_plain: M=%d is beyond 65535 row tiles", M);
     cudaStream_t s = (cudaStream_t)stream;
     if (in_dtype == RMX_F32 && out_dtype == RMX_F32)
-        gemm_plain_kernel<float, float><<<grid, 256, 0, s>>>((const float*)A, (const float*)W, (float*)C, M, N, K, lda, ldw, ldc);
+        gemm_plain_kernel<float, float><<<grid, 256, 0, s>>>((const float*)A, (const float*)W, (float*)C, M, N, K, lda, ldw, ldc, batch_a, batch_w, batch_c);
     else if (in_dtype == RMX_BF16 && out_dtype == RMX_BF16)
         gemm_plain_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, s>>>(
-            (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, (__nv_bfloat16*)C, M, N, K, lda, ldw, ldc);
+            (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, (__nv_bfloat16*)C, M, N, K, lda, ldw, ldc, batch_a, batch_w, batch_c);
     else if (in_dtype == RMX_BF16 && out_dtype == RMX_F32)
         gemm_plain_kernel<__nv_bfloat16, float><<<grid, 256, 0, s>>>((const __nv_bfloat16*)A, (const __nv_bfloat16*)W,
-                                                                  (float*)C, M, N, K, lda, ldw, ldc);
+                                                                  (float*)C, M, N, K, lda, ldw, ldc, batch_a, batch_w, batch_c);
     else
         RMX_FAIL("gemm_plain: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
     RMX_CHECK_LAUNCH("gemm_plain");
     return 0;
+}
+
+RMX_API int rmx_gemm_plain(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw,
+                           int ldc, int in_dtype, int out_dtype, void* stream) {
+    return rmx_gemm_plain_batched(A, W, C, M, N, K, lda, ldw, ldc, 1, 0, 0, 0, in_dtype, out_dtype, stream);
 }

@@ -1,0 +1,268 @@
+// A routed feed-forward (mixture of experts): router, grouping of rows by expert, the experts' products over
+// their groups, and the weighted sum.
+//
+//   z = W_router x (float)            the `top` largest z choose a row's experts; their weights are
+//                                     softmax over the chosen z alone
+//   (row, choice) pairs are sorted by expert, so that every expert's rows are neighbours: `offsets[e]` is where
+//   expert e's run starts, `sorted[p]` is the pair (row * top + choice) at place p, `where[pair]` the place of a pair
+//   the experts' products run over those runs, each tile of rows with its expert's weights
+//   out[row] = sum over choices of weight * y[where[row * top + choice]]  (+ what a shared expert gave)
+//
+// Nothing here waits for the host: counts and offsets stay on the device, grids are sized for the worst case and
+// blocks without work leave at once, so a step can be captured in a graph.  A row's result does not depend on
+// which other rows are in the batch: its router sum, its products (ascending k in one thread) and its weighted
+// sum (ascending choice) have fixed orders.
+#include "common.cuh"
+
+namespace {
+
+// ---- router ---------------------------------------------------------------------------------------------------
+// One warp per row.  Logits in float from the row (in T) and the router's weight (float); ties go to the lower
+// expert.  ids [rows, top], weights [rows, top].
+template <typename T>
+__global__ void moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w, int width, int n_experts,
+                                 int top, int* __restrict__ ids, float* __restrict__ weights, int n_rows) {
+    extern __shared__ float logits_all[];
+    allow_dependents();
+    wait_for_prior_kernels();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (row >= n_rows) return;
+    float* logits = logits_all + warp * n_experts;
+    const T* xr = x + (size_t)row * width;
+    for (int e = 0; e < n_experts; ++e) {
+        const float* we = w + (size_t)e * width;
+        float s = 0.f;
+        for (int i = lane; i < width; i += 32) s = fmaf(to_float(xr[i]), we[i], s);
+        s = warp_sum(s);
+        if (lane == 0) logits[e] = s;
+    }
+    __syncwarp();
+    float first = 0.f, total = 0.f, mine = 0.f;   // lane k keeps the k-th chosen logit (top <= 32)
+    int mine_id = 0;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int best_e = n_experts;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float v = logits[e];
+            if (v > best) { best = v; best_e = e; }      // ascending e: the lowest index of equal values stays
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        }
+        if (best_e >= n_experts) best_e = 0;             // (all values NaN: still a valid expert)
+        if (k == 0) first = best;
+        if (lane == k) { mine = best; mine_id = best_e; }
+        if (lane == 0) logits[best_e] = -INFINITY;
+        __syncwarp();
+    }
+    const float p = lane < top ? expf(mine - first) : 0.f;
+    total = warp_sum(p);
+    if (lane < top) {
+        ids[(size_t)row * top + lane] = mine_id;
+        weights[(size_t)row * top + lane] = p / total;
+    }
+}
+
+// ---- grouping -------------------------------------------------------------------------------------------------
+// One block.  Counting sort of the pairs by expert.
+__global__ void moe_sort_kernel(const int* __restrict__ ids, int total, int n_experts, int* __restrict__ offsets,
+                                int* __restrict__ sorted, int* __restrict__ where) {
+    extern __shared__ int counts[];          // [n_experts] counts, then [n_experts] cursors
+    int* cursor = counts + n_experts;
+    allow_dependents();
+    wait_for_prior_kernels();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < total; i += blockDim.x) atomicAdd(&counts[ids[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            offsets[e] = at;
+            cursor[e] = at;
+            at += counts[e];
+        }
+        offsets[n_experts] = at;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < total; i += blockDim.x) {
+        const int p = atomicAdd(&cursor[ids[i]], 1);
+        sorted[p] = i;
+        where[i] = p;
+    }
+}
+
+// ---- the experts' products ------------------------------------------------------------------------------------
+// C[p, :] = A[row(p), :] . W[e]^T for every place p of expert e's run; row(p) = sorted[p] / divisor when the rows
+// are gathered from the layer's input (divisor = top), p itself when A is already in sorted order (divisor 0).
+// blockIdx.y counts row tiles across all experts; a block finds its expert by walking the offsets.
+// Every output is accumulated by one thread over k in ascending order.
+constexpr int BN = 64, BK = 16;
+
+template <typename TA, typename TC, int BM>
+__global__ void __launch_bounds__(256) moe_gemm_kernel(const TA* __restrict__ A, int lda, const int* __restrict__ sorted,
+                                                       int divisor, const TA* __restrict__ W, TC* __restrict__ C, int ldc,
+                                                       const int* __restrict__ offsets, int n_experts, int N, int K) {
+    constexpr int RM = BM / 16;            // rows per thread
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Ws[BK][BN + 4];
+    __shared__ int rows[BM];
+    allow_dependents();
+    wait_for_prior_kernels();
+    int tile = blockIdx.y, e = 0, begin = 0, end = 0;
+    for (; e < n_experts; ++e) {
+        begin = offsets[e];
+        end = offsets[e + 1];
+        const int tiles = (end - begin + BM - 1) / BM;
+        if (tile < tiles) break;
+        tile -= tiles;
+    }
+    if (e >= n_experts) return;
+    const int m0 = begin + tile * BM;
+    const int n0 = blockIdx.x * BN;
+    const TA* We = W + (size_t)e * N * K;
+    for (int i = threadIdx.x; i < BM; i += 256) {
+        const int p = m0 + i;
+        rows[i] = p < end ? (divisor > 0 ? sorted[p] / divisor : p) : -1;
+    }
+    __syncthreads();
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    float acc[RM][4];
+#pragma unroll
+    for (int i = 0; i < RM; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        for (int idx = threadIdx.x; idx < BM * BK; idx += 256) {
+            const int r = idx / BK, k = k0 + idx % BK;
+            const int src = rows[r];
+            As[idx % BK][r] = (src >= 0 && k < K) ? to_float(A[(size_t)src * lda + k]) : 0.f;
+        }
+        for (int idx = threadIdx.x; idx < BN * BK; idx += 256) {
+            const int r = idx / BK, k = k0 + idx % BK;
+            Ws[idx % BK][r] = (n0 + r < N && k < K) ? to_float(We[(size_t)(n0 + r) * K + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float a[RM], b[4];
+#pragma unroll
+            for (int i = 0; i < RM; ++i) a[i] = As[kk][ty * RM + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < RM; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < RM; ++i) {
+        const int p = m0 + ty * RM + i;
+        if (p >= end) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n < N) C[(size_t)p * ldc + n] = from_float<TC>(acc[i][j]);
+        }
+    }
+}
+
+// ---- the weighted sum -----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ where, const float* __restrict__ weights,
+                                   const T* __restrict__ shared_out, T* __restrict__ out, int top, int width, size_t total) {
+    allow_dependents();
+    wait_for_prior_kernels();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t row = idx / width;
+    const int col = (int)(idx - row * width);
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k)
+        acc = fmaf(weights[row * top + k], to_float(y[(size_t)where[row * top + k] * width + col]), acc);
+    if (shared_out) acc += to_float(shared_out[idx]);
+    out[idx] = from_float<T>(acc);
+}
+}  // namespace
+
+RMX_API int rmx_moe_route(const void* x, const float* w_router, int n_rows, int width, int n_experts, int top, int* ids,
+                          float* weights, int dtype, void* stream) {
+    if (n_rows == 0) return 0;
+    RMX_REQUIRE(n_rows > 0 && width > 0 && n_experts > 0 && top > 0 && top <= n_experts && top <= 32,
+                "moe_route: %d of %d experts (at most 32 a row)", top, n_experts);
+    RMX_REQUIRE(n_experts <= 2048, "moe_route: more than 2048 experts");
+    const int warps = 4;
+    const size_t smem = (size_t)warps * n_experts * sizeof(float);
+    dim3 grid((n_rows + warps - 1) / warps);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RMX_F32)
+        RMX_CHECK_LAUNCHED(launch_dependent(moe_route_kernel<float>, grid, dim3(warps * 32), smem, s, (const float*)x, w_router, width,
+                                            n_experts, top, ids, weights, n_rows), "moe_route");
+    else if (dtype == RMX_BF16)
+        RMX_CHECK_LAUNCHED(launch_dependent(moe_route_kernel<__nv_bfloat16>, grid, dim3(warps * 32), smem, s, (const __nv_bfloat16*)x,
+                                            w_router, width, n_experts, top, ids, weights, n_rows), "moe_route");
+    else
+        RMX_FAIL("moe_route: unknown dtype %d", dtype);
+    return 0;
+}
+
+RMX_API int rmx_moe_sort(const int* ids, int total, int n_experts, int* offsets, int* sorted, int* where, void* stream) {
+    if (total == 0) return 0;
+    RMX_REQUIRE(total > 0 && n_experts > 0 && n_experts <= 2048 && ids && offsets && sorted && where, "moe_sort: bad arguments");
+    RMX_CHECK_LAUNCHED(launch_dependent(moe_sort_kernel, dim3(1), dim3(1024), (size_t)2 * n_experts * sizeof(int), (cudaStream_t)stream,
+                                        ids, total, n_experts, offsets, sorted, where), "moe_sort");
+    return 0;
+}
+
+// total: places in all (rows * top).  W: [n_experts, N, K].  C: [total, N], rows ldc apart.
+RMX_API int rmx_moe_gemm(const void* A, int lda, const int* sorted, int divisor, const void* W, void* C, int ldc,
+                         const int* offsets, int n_experts, int total, int N, int K, int dtype, void* stream) {
+    if (total == 0 || N == 0) return 0;
+    RMX_REQUIRE(total > 0 && N > 0 && K > 0 && n_experts > 0 && lda >= K && ldc >= N, "moe_gemm: bad sizes");
+    RMX_REQUIRE(divisor == 0 || sorted != nullptr, "moe_gemm: gathered rows need the sorted pairs");
+    cudaStream_t s = (cudaStream_t)stream;
+    // few rows an expert (decoding): tiles of 16 rows, so that a tile's work follows the weights it reads
+    const bool small = total <= 16 * n_experts;
+    const int bm = small ? 16 : 64;
+    const int tiles = (total + bm - 1) / bm + n_experts;
+    RMX_REQUIRE(tiles <= 65535, "moe_gemm: too many row tiles (%d)", tiles);
+    dim3 grid((N + BN - 1) / BN, tiles);
+#define RMX_MOE_GEMM(TA, BM_)                                                                                              \
+    RMX_CHECK_LAUNCHED(launch_dependent(moe_gemm_kernel<TA, TA, BM_>, grid, dim3(256), 0, s, (const TA*)A, lda, sorted, divisor, \
+                                        (const TA*)W, (TA*)C, ldc, offsets, n_experts, N, K), "moe_gemm")
+    if (dtype == RMX_F32) {
+        if (small) RMX_MOE_GEMM(float, 16); else RMX_MOE_GEMM(float, 64);
+    } else if (dtype == RMX_BF16) {
+        if (small) RMX_MOE_GEMM(__nv_bfloat16, 16); else RMX_MOE_GEMM(__nv_bfloat16, 64);
+    } else {
+        RMX_FAIL("moe_gemm: unknown dtype %d", dtype);
+    }
+#undef RMX_MOE_GEMM
+    return 0;
+}
+
+RMX_API int rmx_moe_combine(const void* y, const int* where, const float* weights, const void* shared_out, void* out,
+                            int n_rows, int top, int width, int dtype, void* stream) {
+    if (n_rows == 0) return 0;
+    RMX_REQUIRE(n_rows > 0 && top > 0 && width > 0 && y && where && weights && out, "moe_combine: bad arguments");
+    const size_t total = (size_t)n_rows * width;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RMX_F32)
+        RMX_CHECK_LAUNCHED(launch_dependent(moe_combine_kernel<float>, dim3(blocks), dim3(threads), 0, s, (const float*)y, where, weights,
+                                            (const float*)shared_out, (float*)out, top, width, total), "moe_combine");
+    else if (dtype == RMX_BF16)
+        RMX_CHECK_LAUNCHED(launch_dependent(moe_combine_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, s, (const __nv_bfloat16*)y,
+                                            where, weights, (const __nv_bfloat16*)shared_out, (__nv_bfloat16*)out, top, width, total),
+                           "moe_combine");
+    else
+        RMX_FAIL("moe_combine: unknown dtype %d", dtype);
+    return 0;
+}

@@ -37,39 +37,53 @@ template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ h, int width, int vocab, const int* __restrict__ from_last,
                                  const int* __restrict__ seq_index, const int* __restrict__ slots,
-                                 const int* __restrict__ last_tokens) {
+                                 const int* __restrict__ last_tokens, const T* __restrict__ pos_table,
+                                 const int* __restrict__ positions, int max_positions) {
     allow_dependents();        // (what follows waits for this kernel before it touches memory)
     wait_for_prior_kernels();
     const int t = blockIdx.x;
     const int id = (from_last && from_last[t]) ? last_tokens[slots[seq_index[t]]] : ids[t];
     const bool ok = id >= 0 && id < vocab;
     const T* row = table + (size_t)(ok ? id : 0) * width;
+    // a learned vector of the token's position, added in float (a position outside the table adds nothing: the
+    // host refuses such a step before it runs)
+    const int pos = pos_table ? positions[t] : -1;
+    const T* prow = (pos >= 0 && pos < max_positions) ? pos_table + (size_t)pos * width : nullptr;
     float* out = h + (size_t)t * width;
     if ((width & 3) == 0) {  // four numbers per thread and pass
         for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (ok) load4(row + i, v);
+            if (prow) {
+                float4 a;
+                load4(prow + i, a);
+                v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+            }
             *reinterpret_cast<float4*>(out + i) = v;
         }
     } else {
-        for (int i = threadIdx.x; i < width; i += blockDim.x) out[i] = ok ? to_float(row[i]) : 0.f;
+        for (int i = threadIdx.x; i < width; i += blockDim.x)
+            out[i] = (ok ? to_float(row[i]) : 0.f) + (prow ? to_float(prow[i]) : 0.f);
     }
 }
 
 RMX_API int rmx_embedding(const int* ids, const void* table, float* h, int n_tokens, int width, int vocab,
                           const int* from_last, const int* seq_index, const int* slots, const int* last_tokens,
-                          int dtype, void* stream) {
+                          const void* pos_table, const int* positions, int max_positions, int dtype, void* stream) {
     if (n_tokens == 0) return 0;
     RMX_REQUIRE(n_tokens > 0 && width > 0 && vocab > 0, "embedding: bad sizes");
+    RMX_REQUIRE(pos_table == nullptr || (positions && max_positions > 0), "embedding: a position table needs positions and its row count");
     RMX_REQUIRE(from_last == nullptr || (seq_index && slots && last_tokens), "embedding: from_last needs seq_index, slots and last_tokens");
     const int threads = block_threads(width);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RMX_F32)
         RMX_CHECK_LAUNCHED(launch_dependent(embedding_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, ids, (const float*)table, h, width,
-                                            vocab, from_last, seq_index, slots, last_tokens), "embedding");
+                                            vocab, from_last, seq_index, slots, last_tokens, (const float*)pos_table, positions,
+                                            max_positions), "embedding");
     else if (dtype == RMX_BF16)
         RMX_CHECK_LAUNCHED(launch_dependent(embedding_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, ids,
-                                            (const __nv_bfloat16*)table, h, width, vocab, from_last, seq_index, slots, last_tokens), "embedding");
+                                            (const __nv_bfloat16*)table, h, width, vocab, from_last, seq_index, slots, last_tokens,
+                                            (const __nv_bfloat16*)pos_table, positions, max_positions), "embedding");
     else
         RMX_FAIL("embedding: unknown dtype %d", dtype);
     RMX_CHECK_LAUNCH("embedding");
@@ -77,12 +91,12 @@ RMX_API int rmx_embedding(const int* ids, const void* table, float* h, int n_tok
 }
 
 // One block per output row.  src_row = rows ? rows[r] : r.
-//   v = h[src_row] + delta[src_row]          (float; delta may be null)
+//   v = h[src_row] + mult * (delta[src_row] + delta2[src_row])   (float; either delta may be null; mult 1 changes nothing)
 //   if (write_h) h[src_row] = v
 //   x[r] = v * rsqrt(mean(v^2) + eps) * w     (rounded once to T)
 // The reduction order depends on the width and the block size only.
 template <typename T>
-__global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ delta,
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ delta, const T* __restrict__ delta2, float mult,
                                    const int* __restrict__ rows, const float* __restrict__ w, float eps,
                                    T* __restrict__ x, int width, int write_h) {
     __shared__ float scratch[32];
@@ -95,6 +109,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
     const int src = rows ? rows[r] : r;
     float* hrow = h + (size_t)src * width;
     const T* drow = delta ? delta + (size_t)src * width : nullptr;
+    const T* drow2 = delta2 ? delta2 + (size_t)src * width : nullptr;
     T* xrow = x + (size_t)r * width;
     float ss = 0.f;
     if ((width & 3) == 0) {
@@ -103,7 +118,12 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
             if (drow) {
                 float4 d;
                 load4(drow + i, d);
-                v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+                if (drow2) {
+                    float4 e;
+                    load4(drow2 + i, e);
+                    d.x += e.x; d.y += e.y; d.z += e.z; d.w += e.w;
+                }
+                v.x += mult * d.x; v.y += mult * d.y; v.z += mult * d.z; v.w += mult * d.w;
             }
             *reinterpret_cast<float4*>(vals + i) = v;
             if (write_h) *reinterpret_cast<float4*>(hrow + i) = v;
@@ -121,7 +141,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
     } else {
         for (int i = threadIdx.x; i < width; i += blockDim.x) {
             float v = hrow[i];
-            if (drow) v += to_float(drow[i]);
+            if (drow) v += mult * (to_float(drow[i]) + (drow2 ? to_float(drow2[i]) : 0.f));
             vals[i] = v;
             if (write_h) hrow[i] = v;
             ss += v * v;
@@ -135,7 +155,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
 // of four in registers, all their loads under way at once, and the blocks are small enough for several to share an
 // SM.  The reduction order depends on the width and the block size only, as above.
 template <typename T, int CHUNKS>
-__global__ void add_rmsnorm_rows_kernel(float* __restrict__ h, const T* __restrict__ delta,
+__global__ void add_rmsnorm_rows_kernel(float* __restrict__ h, const T* __restrict__ delta, const T* __restrict__ delta2, float mult,
                                         const int* __restrict__ rows, const float* __restrict__ w, float eps,
                                         T* __restrict__ x, int width, int write_h) {
     __shared__ float scratch[32];
@@ -154,6 +174,7 @@ __global__ void add_rmsnorm_rows_kernel(float* __restrict__ h, const T* __restri
     const int src = rows ? rows[r] : r;
     float* hrow = h + (size_t)src * width;
     const T* drow = delta ? delta + (size_t)src * width : nullptr;
+    const T* drow2 = (delta && delta2) ? delta2 + (size_t)src * width : nullptr;
     T* xrow = x + (size_t)r * width;
     float4 v[CHUNKS], d[CHUNKS];
 #pragma unroll
@@ -163,13 +184,19 @@ __global__ void add_rmsnorm_rows_kernel(float* __restrict__ h, const T* __restri
         if (i < width) {
             v[c] = *reinterpret_cast<const float4*>(hrow + i);
             if (drow) load4(drow + i, d[c]);
+            if (drow2) {
+                float4 e;
+                load4(drow2 + i, e);
+                d[c].x += e.x; d[c].y += e.y; d[c].z += e.z; d[c].w += e.w;
+            }
         }
     }
     float ss = 0.f;
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
         const int i = (c * blockDim.x + threadIdx.x) * 4;
-        v[c].x += d[c].x; v[c].y += d[c].y; v[c].z += d[c].z; v[c].w += d[c].w;
+        // (mult is 1 unless the layer scales what it adds to the stream: the product is then exact)
+        v[c].x += mult * d[c].x; v[c].y += mult * d[c].y; v[c].z += mult * d[c].z; v[c].w += mult * d[c].w;
         if (write_h && i < width) *reinterpret_cast<float4*>(hrow + i) = v[c];
         ss += v[c].x * v[c].x;
         ss += v[c].y * v[c].y;
@@ -186,8 +213,8 @@ __global__ void add_rmsnorm_rows_kernel(float* __restrict__ h, const T* __restri
 }
 
 template <typename T>
-int launch_add_rmsnorm(float* h, const T* delta, const int* rows, const float* w, float eps, T* x, int n_rows, int width,
-                       int write_h, cudaStream_t s) {
+int launch_add_rmsnorm(float* h, const T* delta, const T* delta2, float mult, const int* rows, const float* w, float eps, T* x,
+                       int n_rows, int width, int write_h, cudaStream_t s) {
     const int groups = width / 4;
     // Which arrangement runs decides the order in which a row's squares are added.  In the 32-bit path that order
     // may depend on the width only (the same bits however a step is cut), so the number of rows chooses between
@@ -196,7 +223,7 @@ int launch_add_rmsnorm(float* h, const T* delta, const int* rows, const float* w
     if ((width & 3) == 0 && groups <= 1024 && (n_rows <= 256 || !by_rows)) {
         // few rows (decoding): as many threads as the row has groups of four, so that a row's latency is one load
         const int threads = (groups + 31) / 32 * 32;
-        RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_rows_kernel<T, 1>, dim3(n_rows), dim3(threads), 0, s, h, delta, rows, w, eps,
+        RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_rows_kernel<T, 1>, dim3(n_rows), dim3(threads), 0, s, h, delta, delta2, mult, rows, w, eps,
                                             x, width, write_h), "add_rmsnorm");
         return 0;
     }
@@ -205,29 +232,33 @@ int launch_add_rmsnorm(float* h, const T* delta, const int* rows, const float* w
         // many rows: as few threads as hold the row in CHUNKS groups each (at least a warp), several blocks an SM
         int threads = ((groups + CHUNKS - 1) / CHUNKS + 31) / 32 * 32;
         threads = threads < 32 ? 32 : threads;
-        RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_rows_kernel<T, CHUNKS>, dim3(n_rows), dim3(threads), 0, s, h, delta, rows, w, eps,
+        RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_rows_kernel<T, CHUNKS>, dim3(n_rows), dim3(threads), 0, s, h, delta, delta2, mult, rows, w, eps,
                                             x, width, write_h), "add_rmsnorm");
         return 0;
     }
     const int threads = block_threads(width);
     const size_t smem = (size_t)width * sizeof(float);
     if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_kernel<T>, dim3(n_rows), dim3(threads), smem, s, h, delta, rows, w, eps, x, width,
+    RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_kernel<T>, dim3(n_rows), dim3(threads), smem, s, h, delta, delta2, mult, rows, w, eps, x, width,
                                         write_h), "add_rmsnorm");
     return 0;
 }
 
-RMX_API int rmx_add_rmsnorm(float* h, const void* delta, const int* rows, const float* w, float eps, void* x,
-                            int n_rows, int width, int write_h, int dtype, void* stream) {
+// delta2 (or null) and mult: what is added to the stream is mult * (delta + delta2), formed in float (a layer whose
+// mixer and feed-forward read the same norm adds both at once, scaled by the model's factor).
+RMX_API int rmx_add_rmsnorm(float* h, const void* delta, const void* delta2, float mult, const int* rows, const float* w, float eps,
+                            void* x, int n_rows, int width, int write_h, int dtype, void* stream) {
     if (n_rows == 0) return 0;
+    RMX_REQUIRE(delta != nullptr || delta2 == nullptr, "add_rmsnorm: a second delta without a first");
     RMX_REQUIRE(n_rows > 0 && width > 0, "add_rmsnorm: bad sizes");
     RMX_REQUIRE((size_t)width * 4 <= 160 * 1024, "add_rmsnorm: width %d is beyond 40960", width);
     RMX_REQUIRE(!(rows && write_h), "add_rmsnorm: rows and write_h do not go together");
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
-    if (dtype == RMX_F32) rc = launch_add_rmsnorm<float>(h, (const float*)delta, rows, w, eps, (float*)x, n_rows, width, write_h, s);
+    if (dtype == RMX_F32) rc = launch_add_rmsnorm<float>(h, (const float*)delta, (const float*)delta2, mult, rows, w, eps, (float*)x, n_rows, width, write_h, s);
     else if (dtype == RMX_BF16)
-        rc = launch_add_rmsnorm<__nv_bfloat16>(h, (const __nv_bfloat16*)delta, rows, w, eps, (__nv_bfloat16*)x, n_rows, width, write_h, s);
+        rc = launch_add_rmsnorm<__nv_bfloat16>(h, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)delta2, mult, rows, w, eps,
+                                               (__nv_bfloat16*)x, n_rows, width, write_h, s);
     else RMX_FAIL("add_rmsnorm: unknown dtype %d", dtype);
     if (rc != 0) return rc;
     RMX_CHECK_LAUNCH("add_rmsnorm");
@@ -237,6 +268,13 @@ RMX_API int rmx_add_rmsnorm(float* h, const void* delta, const int* rows, const 
 // out[t, j] = silu(gate_up[t, j]) * gate_up[t, inter + j], silu(z) = z / (1 + exp(-z)),
 // in float with one rounding.
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + expf(-g)) * u; }
+// The tanh form of GELU: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), times the other half of the pair.
+__device__ __forceinline__ float gelu_tanh_mul(float g, float u) {
+    const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return 0.5f * g * (1.f + tanhf(inner)) * u;
+}
+// act: 0 silu, 1 the tanh form of GELU
+__device__ __forceinline__ float act_mul(float g, float u, int act) { return act == 1 ? gelu_tanh_mul(g, u) : silu_mul(g, u); }
 
 // Where gate j and up j lie in a row of 2 * inter numbers: concatenated [gate | up] (block == 0), or in blocks of
 // `block` gate numbers followed by their `block` up numbers.
@@ -251,7 +289,7 @@ __device__ __forceinline__ void gate_up_at(int j, int inter, int block, int& gi,
 }
 
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int block, size_t total) {
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int block, size_t total, int act) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t t = idx / inter;
@@ -260,12 +298,12 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
     gate_up_at(j, inter, block, gi, ui);
     const float g = to_float(gate_up[t * 2 * inter + gi]);
     const float u = to_float(gate_up[t * 2 * inter + ui]);
-    out[idx] = from_float<T>(silu_mul(g, u));
+    out[idx] = from_float<T>(act_mul(g, u, act));
 }
 
 // four outputs per thread; inter is a multiple of 4
 template <typename T>
-__global__ void swiglu_kernel4(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int block, size_t total4) {
+__global__ void swiglu_kernel4(const T* __restrict__ gate_up, T* __restrict__ out, int inter, int block, size_t total4, int act) {
     allow_dependents();        // (what follows waits for this kernel before it touches memory)
     wait_for_prior_kernels();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -278,16 +316,22 @@ __global__ void swiglu_kernel4(const T* __restrict__ gate_up, T* __restrict__ ou
     float4 g, u;
     load4(gate_up + t * 2 * inter + gi, g);
     load4(gate_up + t * 2 * inter + ui, u);
-    store4(out + t * inter + j, make_float4(silu_mul(g.x, u.x), silu_mul(g.y, u.y), silu_mul(g.z, u.z), silu_mul(g.w, u.w)));
+    store4(out + t * inter + j, make_float4(act_mul(g.x, u.x, act), act_mul(g.y, u.y, act), act_mul(g.z, u.z, act), act_mul(g.w, u.w, act)));
 }
 
 // bfloat16, sixteen outputs per thread as two groups of eight (16-byte loads and stores); inter and block are
 // multiples of 8.  blockIdx.x is the token, blockIdx.y the part of its row.  The exponential and the division are
 // the fast ones (about two units in the last place of a float): the result is rounded to bfloat16, eight bits.
 __device__ __forceinline__ float silu_mul_fast(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
+// tanh(y) = 1 - 2 / (1 + exp(2y)), so 0.5 g (1 + tanh(y)) = g / (1 + exp(-2y)): the same fast pieces as silu
+__device__ __forceinline__ float gelu_tanh_mul_fast(float g, float u) {
+    const float y2 = 1.5957691216057308f * (g + 0.044715f * g * g * g);
+    return __fdividef(g, 1.f + __expf(-y2)) * u;
+}
+__device__ __forceinline__ float act_mul_fast(float g, float u, int act) { return act == 1 ? gelu_tanh_mul_fast(g, u) : silu_mul_fast(g, u); }
 
 __global__ void swiglu_kernel8(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter,
-                               int block) {
+                               int block, int act) {
     allow_dependents();        // (what follows waits for this kernel before it touches memory)
     wait_for_prior_kernels();
     const int per_row = inter >> 3;
@@ -315,16 +359,18 @@ __global__ void swiglu_kernel8(const __nv_bfloat16* __restrict__ gate_up, __nv_b
         for (int i = 0; i < 4; ++i) {
             const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[i]));
             const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[i]));
-            __nv_bfloat162 r = __floats2bfloat162_rn(silu_mul_fast(a.x, b.x), silu_mul_fast(a.y, b.y));
+            __nv_bfloat162 r = __floats2bfloat162_rn(act_mul_fast(a.x, b.x, act), act_mul_fast(a.y, b.y, act));
             ow[i] = *reinterpret_cast<uint32_t*>(&r);
         }
         *reinterpret_cast<uint4*>(dst + j[c]) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
 }
 
-RMX_API int rmx_swiglu(const void* gate_up, void* out, int n_tokens, int inter, int block, int dtype, void* stream) {
+// act: which function the gate goes through before it multiplies the up half: 0 silu, 1 the tanh form of GELU.
+RMX_API int rmx_swiglu(const void* gate_up, void* out, int n_tokens, int inter, int block, int act, int dtype, void* stream) {
     if (n_tokens == 0) return 0;
     RMX_REQUIRE(n_tokens > 0 && inter > 0, "swiglu: bad sizes");
+    RMX_REQUIRE(act == 0 || act == 1, "swiglu: unknown activation %d", act);
     RMX_REQUIRE(block == 0 || (block > 0 && inter % block == 0), "swiglu: blocks of %d do not divide %d", block, inter);
     const bool vec = (inter & 3) == 0 && (block & 3) == 0;
     const int threads = 256;
@@ -333,17 +379,17 @@ RMX_API int rmx_swiglu(const void* gate_up, void* out, int n_tokens, int inter, 
         const int per_row = inter / 8;
         const int t8 = per_row >= 512 ? 256 : 128;
         RMX_CHECK_LAUNCHED(launch_dependent(swiglu_kernel8, dim3(n_tokens, (per_row + 2 * t8 - 1) / (2 * t8)), dim3(t8), 0, s,
-                                            (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block), "swiglu");
+                                            (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, act), "swiglu");
         return 0;
     }
     const size_t total = (size_t)n_tokens * inter / (vec ? 4 : 1);
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
     if (dtype == RMX_F32) {
-        if (vec) RMX_CHECK_LAUNCHED(launch_dependent(swiglu_kernel4<float>, dim3(blocks), dim3(threads), 0, s, (const float*)gate_up, (float*)out, inter, block, total), "swiglu");
-        else swiglu_kernel<float><<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, inter, block, total);
+        if (vec) RMX_CHECK_LAUNCHED(launch_dependent(swiglu_kernel4<float>, dim3(blocks), dim3(threads), 0, s, (const float*)gate_up, (float*)out, inter, block, total, act), "swiglu");
+        else swiglu_kernel<float><<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, inter, block, total, act);
     } else if (dtype == RMX_BF16) {
-        if (vec) RMX_CHECK_LAUNCHED(launch_dependent(swiglu_kernel4<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, s, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total), "swiglu");
-        else swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total);
+        if (vec) RMX_CHECK_LAUNCHED(launch_dependent(swiglu_kernel4<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, s, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total, act), "swiglu");
+        else swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total, act);
     } else {
         RMX_FAIL("swiglu: unknown dtype %d", dtype);
     }

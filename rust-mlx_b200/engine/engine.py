@@ -176,6 +176,10 @@ class Engine:
                     self.pools.open(rid)
                     opened.append((key, rid))
                 start = table.length(rid)
+                rows = getattr(self.spec.embedding, "max_positions", 0)
+                if rows and start + len(tokens) > rows:
+                    raise EngineError(f"request {key!r} would reach position {start + len(tokens) - 1}; the model's "
+                                      f"position table has {rows} rows")
                 table.reserve(rid, start + len(tokens))
                 seqs.append(SequenceInput(rid, start, list(tokens), list(want)))
             batch = build_batch(seqs, self.pools, self.device, self._status, self.vocab_size)

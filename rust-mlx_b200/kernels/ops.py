@@ -54,27 +54,36 @@ def count_launches(n: int) -> None:
     _launched(n)
 
 
-def embedding(ids, table, h_out, from_last=None, seq_index=None, slots=None, last_tokens=None):
+def embedding(ids, table, h_out, from_last=None, seq_index=None, slots=None, last_tokens=None, pos_table=None,
+              positions=None):
     """h_out[t] = table[ids[t]] as float32 (the residual stream).  Where from_last[t] is set the id is the one the
-    last step's sampling left for the token's sequence: last_tokens[slots[seq_index[t]]]."""
+    last step's sampling left for the token's sequence: last_tokens[slots[seq_index[t]]].  With ``pos_table`` the
+    learned vector of the token's position, pos_table[positions[t]], is added (in float)."""
     lib = kernels_library()
     n, width = h_out.shape
+    if pos_table is not None and (pos_table.dtype != table.dtype or pos_table.shape[1] != width):
+        raise KernelError("embedding: the position table must have the token table's dtype and width")
     check(lib.rmx_embedding(_ptr(ids, torch.int32, "ids"), _ptr(table, name="table"), _ptr(h_out, torch.float32, "h"),
                             c_int(n), c_int(width), c_int(table.shape[0]), _ptr(from_last, torch.int32, "from_last"),
                             _ptr(seq_index, torch.int32, "seq_index"), _ptr(slots, torch.int32, "slots"),
-                            _ptr(last_tokens, torch.int32, "last_tokens"), c_int(dtype_code(table)), _stream()))
+                            _ptr(last_tokens, torch.int32, "last_tokens"), _ptr(pos_table, name="pos_table"),
+                            _ptr(positions if pos_table is not None else None, torch.int32, "positions"),
+                            c_int(pos_table.shape[0] if pos_table is not None else 0), c_int(dtype_code(table)), _stream()))
     _launched()
 
 
-def add_rmsnorm(h, delta, weight, eps, x_out, rows=None, write_h=True):
-    """v = h + delta; h = v (if write_h); x_out = RMSNorm(v; weight, eps).  With ``rows`` the
+def add_rmsnorm(h, delta, weight, eps, x_out, rows=None, write_h=True, delta2=None, mult=1.0):
+    """v = h + mult * (delta + delta2); h = v (if write_h); x_out = RMSNorm(v; weight, eps).  With ``rows`` the
     rows rows[r] are read, x_out[r] is written and h is left alone."""
     lib = kernels_library()
     n = x_out.shape[0]
     width = h.shape[1]
     if delta is not None and delta.dtype != x_out.dtype:
         raise KernelError("add_rmsnorm: delta and output must have the same dtype")
-    check(lib.rmx_add_rmsnorm(_ptr(h, torch.float32, "h"), _ptr(delta, name="delta"), _ptr(rows, torch.int32, "rows"),
+    if delta2 is not None and (delta is None or delta2.dtype != delta.dtype or delta2.shape != delta.shape):
+        raise KernelError("add_rmsnorm: a second delta goes with a first of the same shape and dtype")
+    check(lib.rmx_add_rmsnorm(_ptr(h, torch.float32, "h"), _ptr(delta, name="delta"), _ptr(delta2, name="delta2"), c_float(mult),
+                              _ptr(rows, torch.int32, "rows"),
                               _ptr(weight, torch.float32, "weight"), c_float(eps), _ptr(x_out, name="x"),
                               c_int(n), c_int(width), c_int(1 if (write_h and rows is None) else 0),
                               c_int(dtype_code(x_out)), _stream()))
@@ -98,15 +107,133 @@ def add_bias(x, bias):
     _launched()
 
 
-def swiglu(gate_up, out, block=0):
-    """out = silu(gate) * up.  A row of ``gate_up`` is [gate | up] (block 0) or blocks of ``block``
-    gate numbers each followed by its ``block`` up numbers."""
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def swiglu(gate_up, out, block=0, activation="silu"):
+    """out = act(gate) * up, act = silu or the tanh form of GELU.  A row of ``gate_up`` is [gate | up] (block 0) or
+    blocks of ``block`` gate numbers each followed by its ``block`` up numbers."""
     lib = kernels_library()
     n, inter = out.shape
     if gate_up.shape != (n, 2 * inter) or gate_up.dtype != out.dtype:
         raise KernelError("swiglu: gate_up must be [tokens, 2 * inter] of the output's dtype")
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"swiglu: unknown activation {activation!r}: {sorted(ACTIVATIONS)}")
     check(lib.rmx_swiglu(_ptr(gate_up, name="gate_up"), _ptr(out, name="out"), c_int(n), c_int(inter), c_int(block),
-                         c_int(dtype_code(out)), _stream()))
+                         c_int(ACTIVATIONS[activation]), c_int(dtype_code(out)), _stream()))
+    _launched()
+
+
+def _rows_view(t, name):
+    """[rows, heads, size] with unit stride along ``size`` and heads side by side in a row (a view of [rows, heads * size]
+    or of some columns of wider rows): (pointer, row stride, head stride)."""
+    if t.dim() != 3 or t.stride(2) != 1 or not t.is_cuda:
+        raise KernelError(f"{name} must be [rows, heads, size] on a CUDA device with unit stride along size")
+    return c_void_p(t.data_ptr()), t.stride(0), t.stride(1)
+
+
+def gemm_plain_heads(a, w, out):
+    """out[t, h, :] = w[h] . a[t, h, :] for every head h on the FMA units (k ascending): a [rows, heads, K],
+    w [heads, N, K] contiguous, out [rows, heads, N]."""
+    lib = kernels_library()
+    m, heads, k = a.shape
+    n = w.shape[1]
+    if w.shape != (heads, n, k) or out.shape != (m, heads, n) or a.dtype != w.dtype or not w.is_contiguous():
+        raise KernelError(f"gemm_plain_heads: {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
+    pa, lda, ba = _rows_view(a, "a")
+    pc, ldc, bc = _rows_view(out, "out")
+    ll = ctypes.c_longlong
+    check(lib.rmx_gemm_plain_batched(pa, _ptr(w, name="w"), pc, c_int(m), c_int(n), c_int(k), c_int(lda), c_int(k), c_int(ldc),
+                                     c_int(heads), ll(ba), ll(n * k), ll(bc), c_int(dtype_code(a)), c_int(dtype_code(out)), _stream()))
+    _launched()
+
+
+def latent_norms(proj, q_rank, kv_rank, q_weight, kv_weight, eps, cq_out, pool, positions, seq_index, block_table, page_size,
+                 status):
+    """Rows of ``proj`` are [query latent | key/value latent | ...]: cq_out = RMSNorm(query latent; q_weight), and
+    (``pool`` given, kv_rank > 0) RMSNorm(key/value latent; kv_weight) goes into the token's place in ``pool``
+    [pages, 1, page_size, kv_rank] through its sequence's block table."""
+    lib = kernels_library()
+    n = proj.shape[0]
+    if proj.dim() != 2 or proj.stride(1) != 1 or cq_out.shape != (n, q_rank) or cq_out.dtype != proj.dtype:
+        raise KernelError("latent_norms: proj must be [tokens, columns] with unit column stride, cq_out [tokens, q_rank] of its dtype")
+    write = pool is not None and kv_rank > 0
+    check(lib.rmx_latent_norms(
+        c_void_p(proj.data_ptr()), c_int(proj.stride(0)), c_int(q_rank), c_int(kv_rank if write else 0),
+        _ptr(q_weight, torch.float32, "q_weight"), _ptr(kv_weight if write else None, torch.float32, "kv_weight"), c_float(eps),
+        _ptr(cq_out, name="cq_out"), _ptr(pool if write else None, proj.dtype, "pool"),
+        _ptr(positions, torch.int32, "positions"), _ptr(seq_index, torch.int32, "seq_index"),
+        _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), c_int(page_size), c_int(n),
+        _ptr(status, torch.int32, "status"), c_int(dtype_code(proj)), _stream()))
+    _launched()
+
+
+def gate_heads(o, gate, heads, vdim):
+    """o[t, h, :] *= sigmoid(gate[t, h]) in place.  ``gate`` may be some columns of wider rows."""
+    lib = kernels_library()
+    n = o.shape[0]
+    if o.shape != (n, heads * vdim) or gate.shape != (n, heads) or gate.stride(1) != 1 or gate.dtype != o.dtype:
+        raise KernelError("gate_heads: o must be [tokens, heads * vdim], gate [tokens, heads] of the same dtype")
+    check(lib.rmx_gate_heads(_ptr(o, name="o"), c_void_p(gate.data_ptr()), c_int(gate.stride(0)), c_int(n), c_int(heads),
+                             c_int(vdim), c_int(dtype_code(o)), _stream()))
+    _launched()
+
+
+def moe_route(x, w_router, top, ids_out, weights_out):
+    """Router of a mixture of experts: logits = x . w_router^T in float; per row the ``top`` largest choose the
+    experts (ids_out [rows, top] int32), weights_out = softmax over the chosen logits."""
+    lib = kernels_library()
+    n, width = x.shape
+    e = w_router.shape[0]
+    if w_router.shape != (e, width) or ids_out.shape != (n, top) or weights_out.shape != (n, top):
+        raise KernelError("moe_route: shapes do not fit")
+    check(lib.rmx_moe_route(_ptr(x, name="x"), _ptr(w_router, torch.float32, "w_router"), c_int(n), c_int(width), c_int(e),
+                            c_int(top), _ptr(ids_out, torch.int32, "ids"), _ptr(weights_out, torch.float32, "weights"),
+                            c_int(dtype_code(x)), _stream()))
+    _launched()
+
+
+def moe_sort(ids, n_experts, offsets_out, sorted_out, where_out):
+    """Group the (row, choice) pairs of ``ids`` [rows, top] by expert: offsets_out [experts + 1], sorted_out[p] = the
+    pair at place p, where_out[pair] = its place."""
+    lib = kernels_library()
+    total = ids.numel()
+    if offsets_out.numel() != n_experts + 1 or sorted_out.numel() != total or where_out.numel() != total:
+        raise KernelError("moe_sort: shapes do not fit")
+    check(lib.rmx_moe_sort(_ptr(ids, torch.int32, "ids"), c_int(total), c_int(n_experts), _ptr(offsets_out, torch.int32, "offsets"),
+                           _ptr(sorted_out, torch.int32, "sorted"), _ptr(where_out, torch.int32, "where"), _stream()))
+    _launched()
+
+
+def moe_gemm(a, w, out, offsets, sorted_pairs=None, top=0):
+    """out[p] = w[e] . a[row(p)] for every place p of expert e's run (``offsets``).  ``w`` [experts, N, K].  With
+    ``sorted_pairs`` and ``top`` the rows are gathered from the layer's input (row(p) = sorted_pairs[p] // top), else
+    ``a`` is already in sorted order."""
+    lib = kernels_library()
+    e, n, k = w.shape
+    total = out.shape[0]
+    if a.shape[1] != k or out.shape != (total, n) or a.dtype != w.dtype or out.dtype != a.dtype or not w.is_contiguous():
+        raise KernelError(f"moe_gemm: {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
+    if sorted_pairs is None and a.shape[0] != total:
+        raise KernelError("moe_gemm: rows in sorted order must be as many as the output's")
+    check(lib.rmx_moe_gemm(_ptr(a, name="a"), c_int(a.stride(0)), _ptr(sorted_pairs, torch.int32, "sorted"),
+                           c_int(top if sorted_pairs is not None else 0), _ptr(w, name="w"), _ptr(out, name="out"),
+                           c_int(out.stride(0)), _ptr(offsets, torch.int32, "offsets"), c_int(e), c_int(total), c_int(n), c_int(k),
+                           c_int(dtype_code(a)), _stream()))
+    _launched()
+
+
+def moe_combine(y, where, weights, shared_out, out):
+    """out[row] = sum over choices of weights[row, choice] * y[where[row, choice]] (+ shared_out[row]), summed in float
+    in the order of the choices."""
+    lib = kernels_library()
+    n, width = out.shape
+    top = weights.shape[1]
+    if y.shape != (n * top, width) or where.numel() != n * top or (shared_out is not None and shared_out.shape != out.shape):
+        raise KernelError("moe_combine: shapes do not fit")
+    check(lib.rmx_moe_combine(_ptr(y, out.dtype, "y"), _ptr(where, torch.int32, "where"), _ptr(weights, torch.float32, "weights"),
+                              _ptr(shared_out, out.dtype if shared_out is not None else None, "shared"), _ptr(out, name="out"),
+                              c_int(n), c_int(top), c_int(width), c_int(dtype_code(out)), _stream()))
     _launched()
 
 
@@ -645,6 +772,16 @@ class Kernels:
             torch.mm(x, w.t(), out=out)
         else:
             torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+
+    def linear_heads(self, a, w, out):
+        """out[t, h, :] = w[h] . a[t, h, :]: every head's rows with that head's own matrix.  a [rows, heads, K] and out
+        [rows, heads, N] are views with the heads side by side in a row; w [heads, N, K].  float32: the plain kernel
+        (k ascending); bfloat16: the library's batched product with float accumulation, on the strided views as
+        they are."""
+        if a.dtype == torch.float32:
+            gemm_plain_heads(a, w, out)
+        else:
+            torch.bmm(a.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
 
     def gemm_tcgen05(self, a, w, out, workspace=None, status=None, splits=None, cluster=True, dependent=False, swiglu=False):
         """The tcgen05 product with the number of K slices that this engine's tuning found best for the shape."""

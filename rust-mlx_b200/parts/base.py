@@ -45,7 +45,8 @@ class CacheSpec:
 
     kind "paged": keys and values per token, ``kv_heads`` x ``head_dim`` each, in
     pages; ``window`` > 0 means only the last ``window`` positions are ever read, so
-    older pages can be given back.  kind "state": ``state_shape`` numbers of
+    older pages can be given back.  ``values=False``: one pool only (a mixer that keeps a
+    single latent per token, from which it forms keys and values alike).  kind "state": ``state_shape`` numbers of
     ``state_dtype`` per request, of fixed size, zero when a request starts.
     Layers with equal specs share a cache group (one page pool geometry, one block
     table per request).
@@ -57,10 +58,11 @@ class CacheSpec:
     window: int = 0
     state_shape: tuple = ()
     state_dtype: str = "float32"
+    values: bool = True
 
     def group_key(self) -> tuple:
         if self.kind == "paged":
-            return ("paged", self.kv_heads, self.head_dim, self.window)
+            return ("paged", self.kv_heads, self.head_dim, self.window) + (() if self.values else ("no values",))
         return ("state", self.state_shape, self.state_dtype)
 
 
@@ -86,6 +88,17 @@ class DecodeShape:
 
     n_seqs: int
     max_seq_len: int
+
+
+@dataclass
+class ScaledSum:
+    """What a block leaves to be added to the residual stream when it is not one tensor: factor * (first + second),
+    formed in float by the norm that adds it (``second`` may be None).  A block whose mixer and feed-forward read
+    the same normed rows hands both outputs on like this."""
+
+    first: torch.Tensor
+    second: Optional[torch.Tensor] = None
+    factor: float = 1.0
 
 
 class Part:
@@ -142,7 +155,7 @@ class Part:
 
 
 class Norm(Part):
-    """``forward(h, delta) -> (h, x)``: adds ``delta`` (or nothing) to the 32-bit residual
+    """``forward(h, delta) -> (h, x)``: adds ``delta`` (a tensor, a ``ScaledSum`` or nothing) to the 32-bit residual
     stream ``h`` in place and returns the normalised rows in the compute dtype."""
 
     def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor]):

@@ -1,6 +1,7 @@
 """How a mixer, a feed-forward and their norms are arranged in a layer.
 
 ``PreNormBlock``: h += mixer(norm1(h)); h += ffn(norm2(h)) (src/dense.rs:380-390).
+``ParallelBlock``: x = norm(h); h += factor * (mixer(x) + ffn(x)): one norm, both sublayers read it.
 The residual stream is float32.  A block receives the stream together with a
 pending delta (the previous block's last output, not yet added) so that every
 add is fused with the norm that follows it; it returns the stream and its own
@@ -8,7 +9,7 @@ pending delta.
 """
 from __future__ import annotations
 
-from .base import Part
+from .base import Part, ScaledSum
 
 
 class PreNormBlock(Part):
@@ -39,3 +40,36 @@ class PreNormBlock(Part):
         if tap is not None:
             tap("ffn_out", m)
         return h, m
+
+
+class ParallelBlock(Part):
+    """One norm whose rows the mixer and the feed-forward both read; what they give is added to the stream together,
+    times ``factor``: h <- h + factor * (mixer(norm(h)) + ffn(norm(h))).  ``ffn`` may be None (a layer of a mixer
+    alone).  The sum is formed in float by the norm that adds it (the next block's, or the model's last)."""
+
+    graph_safe = True
+
+    def __init__(self, norm, mixer, ffn=None, factor: float = 1.0):
+        self.norm, self.mixer, self.ffn, self.factor = norm, mixer, ffn, float(factor)
+
+    def children(self):
+        return [self.norm, self.mixer] + ([self.ffn] if self.ffn is not None else [])
+
+    def cache_specs(self):
+        return self.mixer.cache_specs()
+
+    def forward(self, h, pending, batch, cache):
+        tap = self.ctx.tap
+        h, x = self.norm.forward(h, pending)
+        if tap is not None:
+            tap("residual", h)
+            tap("norm1", x)
+        a = self.mixer.forward(x, batch, cache)
+        if tap is not None:
+            tap("mixer_out", a)
+        m = None
+        if self.ffn is not None:
+            m = self.ffn.forward(x, batch)
+            if tap is not None:
+                tap("ffn_out", m)
+        return h, ScaledSum(a, m, self.factor)

@@ -36,6 +36,33 @@ class TokenEmbedding(Part):
         return h
 
 
+class PositionedEmbedding(TokenEmbedding):
+    """Token rows plus a learned vector per position: h[t] = table[id_t] + positions_table[p_t], p_t counted from 0
+    in each sequence, added unscaled in float.  ``max_positions`` rows: the longest sequence the model takes."""
+
+    def __init__(self, name: str, vocab: int, width: int, position_name: str, max_positions: int):
+        super().__init__(name, vocab, width)
+        self.position_name, self.max_positions = position_name, int(max_positions)
+        self.position_table = None
+
+    def param_specs(self):
+        return super().param_specs() + [ParamSpec(self.position_name, (self.max_positions, self.width), "embedding")]
+
+    def bind(self, tensors, ctx):
+        super().bind(tensors, ctx)
+        self.position_table = tensors[self.position_name].contiguous()
+
+    def forward(self, ids, batch=None):
+        if batch is None:
+            raise ValueError("an embedding with learned positions needs the batch's positions")
+        h = self.ctx.workspace.get("residual", (ids.shape[0], self.width), torch.float32)
+        last = batch.last_tokens is not None
+        self.ctx.ops.embedding(ids, self.weight, h, batch.from_last if last else None, batch.seq_index if last else None,
+                               batch.slots if last else None, batch.last_tokens, pos_table=self.position_table,
+                               positions=batch.positions)
+        return h
+
+
 class OutputHead(Part):
     graph_safe = True
 

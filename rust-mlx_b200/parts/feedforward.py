@@ -1,4 +1,4 @@
-"""The dense feed-forward: down(silu(gate(x)) * up(x)) (src/dense.rs:293-298).
+"""The gated feed-forward: down(act(gate(x)) * up(x)), act = silu (src/dense.rs:293-298) or the tanh form of GELU.
 
 gate and up are one matrix product over fused weights: blocks of 64 gate rows each
 followed by their 64 up rows (plain concatenation when the width is no multiple of
@@ -15,22 +15,29 @@ from .base import FeedForward, ParamSpec
 
 
 class SwiGLUFeedForward(FeedForward):
+    """``activation``: "silu" or "gelu_tanh".  ``names``: the tensor names of gate, up and down below ``prefix``
+    (checkpoints of other families call them otherwise)."""
+
     graph_safe = True
 
-    def __init__(self, prefix: str, width: int, inner: int):
+    def __init__(self, prefix: str, width: int, inner: int, activation: str = "silu",
+                 names: tuple = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")):
+        if activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"unknown activation {activation!r}")
         self.prefix, self.width, self.inner = prefix, int(width), int(inner)
+        self.activation = activation
+        self.names = tuple(f"{prefix}.{n}" for n in names)
         self.w_gate_up = self.w_down = None
 
     def param_specs(self):
-        p = self.prefix
-        return [ParamSpec(f"{p}.gate_proj.weight", (self.inner, self.width)),
-                ParamSpec(f"{p}.up_proj.weight", (self.inner, self.width)),
-                ParamSpec(f"{p}.down_proj.weight", (self.width, self.inner))]
+        gate, up, down = self.names
+        return [ParamSpec(gate, (self.inner, self.width)),
+                ParamSpec(up, (self.inner, self.width)),
+                ParamSpec(down, (self.width, self.inner))]
 
     def bind(self, tensors, ctx):
         super().bind(tensors, ctx)
-        p = self.prefix
-        gate, up = tensors.pop(f"{p}.gate_proj.weight"), tensors.pop(f"{p}.up_proj.weight")
+        gate, up = tensors.pop(self.names[0]), tensors.pop(self.names[1])
         self.block = 64 if self.inner % 64 == 0 else 0
         if self.block:
             g = gate.view(self.inner // 64, 64, self.width)
@@ -38,27 +45,29 @@ class SwiGLUFeedForward(FeedForward):
             self.w_gate_up = torch.stack([g, u], dim=1).reshape(2 * self.inner, self.width).contiguous()
         else:
             self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
-        self.w_down = tensors[f"{p}.down_proj.weight"].contiguous()
+        self.w_down = tensors[self.names[2]].contiguous()
 
     def linear_weights(self):
         return [self.w_gate_up, self.w_down]
 
     def gate_up_weights(self):
-        return [self.w_gate_up] if self.block else []
+        return [self.w_gate_up] if self.block and self.activation == "silu" else []
 
-    def forward(self, x, batch=None):
+    def forward(self, x, batch=None, out_name: str = "ffn_out"):
         ops, ws, dt = self.ctx.ops, self.ctx.workspace, self.ctx.dtype
         n = x.shape[0]
         status = batch.status if batch is not None else None
         act = ws.get("ffn_act", (n, self.inner), dt)
-        if self.block and dt == torch.bfloat16 and ops.prefers_fused_swiglu(n, 2 * self.inner, self.width):
+        # (the product's own epilogue knows silu only)
+        if (self.block and dt == torch.bfloat16 and self.activation == "silu"
+                and ops.prefers_fused_swiglu(n, 2 * self.inner, self.width)):
             ops.gemm_tcgen05(x, self.w_gate_up, act, ws, status, dependent=ops.dependent_launch, swiglu=True)
         else:
             gu = ws.get("gate_up", (n, 2 * self.inner), dt)
             ops.linear(x, self.w_gate_up, gu, ws, status)
-            ops.swiglu(gu, act, self.block)
+            ops.swiglu(gu, act, self.block, self.activation)
         if self.ctx.tap is not None:
             self.ctx.tap("ffn_act", act)
-        y = ws.get("ffn_out", (n, self.width), dt)
+        y = ws.get(out_name, (n, self.width), dt)
         ops.linear(act, self.w_down, y, ws, status)
         return y

@@ -8,7 +8,14 @@ checkpoint) so both paths read the same numbers.
 """
 from __future__ import annotations
 
-from .base import Norm, ParamSpec
+from .base import Norm, ParamSpec, ScaledSum
+
+
+def _terms(delta):
+    """(first, second, factor) of what is to be added to the stream."""
+    if isinstance(delta, ScaledSum):
+        return delta.first, delta.second, delta.factor
+    return delta, None, 1.0
 
 
 class RMSNorm(Norm):
@@ -27,10 +34,12 @@ class RMSNorm(Norm):
 
     def forward(self, h, delta):
         x = self.ctx.workspace.get("norm_out", (h.shape[0], self.width), self.ctx.dtype)
-        self.ctx.ops.add_rmsnorm(h, delta, self.weight, self.eps, x)
+        first, second, factor = _terms(delta)
+        self.ctx.ops.add_rmsnorm(h, first, self.weight, self.eps, x, delta2=second, mult=factor)
         return h, x
 
     def forward_rows(self, h, delta, rows):
         x = self.ctx.workspace.get("norm_rows_out", (rows.shape[0], self.width), self.ctx.dtype)
-        self.ctx.ops.add_rmsnorm(h, delta, self.weight, self.eps, x, rows=rows)
+        first, second, factor = _terms(delta)
+        self.ctx.ops.add_rmsnorm(h, first, self.weight, self.eps, x, rows=rows, delta2=second, mult=factor)
         return x

@@ -42,7 +42,7 @@ def known_architectures() -> list:
 def find_architecture(raw: dict) -> Architecture:
     """The entry that a config.json (as a dict) names."""
     _load_builtin()
-    names = raw.get("architectures") or []
+    names = raw.get("architectures") or raw.get("architecture") or []     # (some families name one, in the singular)
     if isinstance(names, str):
         names = [names]
     for n in names:
@@ -75,4 +75,4 @@ def _load_builtin() -> None:
     global _loaded
     if not _loaded:
         _loaded = True
-        from .models import qwen3  # noqa: F401  (registers itself)
+        from .models import qwen3, resolorn  # noqa: F401  (they register themselves)
