@@ -358,6 +358,271 @@ def continuous(cfg, raw, a):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# --family resolorn: the Resolorn design at layer sizes of real models, beside the Qwen3 dense decoder of equal
+# width, depth, head size and feed-forward width: decode and prefill throughput, and every phase of a step against
+# its roofline (bytes over the measured copy bandwidth, or flops over the measured product peak, whichever is slower).
+
+def _latent_mixer(heads, dim, vdim, q_rank, kv_rank, window=0, kv_from=None):
+    m = {"heads": heads, "dim": dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank, "scale": dim ** -0.5}
+    if window:
+        m["mask"] = {"size": window}
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return m
+
+
+def resolorn_shape(width, heads, dim, q_rank, kv_rank, ff, experts, top, expert_ff, shared_ff, vocab, window, groups=1):
+    """Groups of four layers: dense and routed feed-forwards in turn; the second pair reads the latents of the first
+    routed layer; the first and third have a window."""
+    layers = []
+    for g in range(groups):
+        base = 4 * g
+        dense = {"kind": "dense", "ff": ff}
+        moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}, "shared": {"ff": shared_ff}}
+        layers += [{"type": "latent_attention", "mixer": _latent_mixer(heads, dim, dim, q_rank, kv_rank, window), "mlp": dense},
+                   {"type": "latent_attention", "mixer": _latent_mixer(heads, dim, dim, q_rank, kv_rank), "mlp": moe},
+                   {"type": "latent_attention", "mixer": _latent_mixer(heads, dim, dim, q_rank, kv_rank, window, kv_from=base + 1), "mlp": dense},
+                   {"type": "latent_attention", "mixer": _latent_mixer(heads, dim, dim, q_rank, kv_rank, kv_from=base + 1), "mlp": moe}]
+    return {"architecture": "Resolorn", "vocab": vocab, "width": width, "max_positions": 2 * MAX_CONTEXT, "norm": {"eps": 1e-6},
+            "residual_mult": 0.5, "layers": layers}
+
+
+FAMILY_SIZES = {
+    # width, heads, dim, q_rank, kv_rank, dense ff, experts, top, expert ff, shared ff, vocab, window
+    "2k": dict(width=2048, heads=16, dim=64, q_rank=512, kv_rank=128, ff=8192, experts=32, top=4, expert_ff=1024, shared_ff=1024,
+               vocab=32768, window=1024),
+    "4k": dict(width=4096, heads=16, dim=128, q_rank=1536, kv_rank=128, ff=12288, experts=64, top=6, expert_ff=1408, shared_ff=2816,
+               vocab=65536, window=1024),
+}
+
+
+def _product(n, rows, cols):
+    """(bytes, flops) of [n, cols] . [rows, cols]^T in bfloat16."""
+    return 2.0 * (rows * cols + n * cols + n * rows), 2.0 * n * rows * cols
+
+
+def _keys_seen(starts, counts, window):
+    """Sum over the step's tokens of the keys each sees (itself and those before it, inside its window)."""
+    total = 0
+    for s, c in zip(starts, counts):
+        for p in range(s, s + c):
+            total += min(p + 1, window) if window else p + 1
+    return total
+
+
+def resolorn_costs(raw, starts, counts):
+    """tap name -> function(layer) -> (bytes, flops) of the kernels that end at that tap, for a step whose sequences hold
+    ``starts`` tokens and bring ``counts`` more."""
+    n, W = sum(counts), raw["width"]
+
+    def cached(layer):      # latents read: every sequence's visible keys once (all heads share them)
+        window = (layer["mixer"].get("mask") or {}).get("size", 0)
+        return sum(min(s + c, window + c - 1) if window else s + c for s, c in zip(starts, counts))
+
+    def mix(f):
+        return lambda layer: f(layer["mixer"], layer)
+
+    def mlp(f):
+        return lambda layer: f(layer["mlp"], layer)
+
+    def touched(f):         # experts whose weights a step reads, if rows choose uniformly
+        e, top = f["router"]["experts"], f["router"]["top"]
+        return e * (1.0 - (1.0 - top / e) ** n)
+
+    return {
+        "norm1": lambda layer: (n * W * 14.0, 0.0),
+        "latent_down": mix(lambda m, layer: _product(n, m["q_rank"] + (0 if "kv_from" in m else m["kv_rank"]) + m["heads"], W)),
+        "latent_q": mix(lambda m, layer: (4.0 * n * (m["q_rank"] + (0 if "kv_from" in m else m["kv_rank"])), 0.0)),
+        "q_heads": mix(lambda m, layer: _product(n, m["heads"] * m["dim"], m["q_rank"])),
+        "q_latent": mix(lambda m, layer: (2.0 * m["heads"] * (m["dim"] * m["kv_rank"] + n * (m["dim"] + m["kv_rank"])),
+                                          2.0 * n * m["heads"] * m["dim"] * m["kv_rank"])),
+        "attn_out": mix(lambda m, layer: (2.0 * cached(layer) * m["kv_rank"] + 4.0 * n * m["heads"] * m["kv_rank"],
+                                          4.0 * _keys_seen(starts, counts, (m.get("mask") or {}).get("size", 0)) * m["heads"] * m["kv_rank"])),
+        "attn_values": mix(lambda m, layer: (2.0 * m["heads"] * (m["vdim"] * m["kv_rank"] + n * (m["vdim"] + m["kv_rank"])),
+                                             2.0 * n * m["heads"] * m["vdim"] * m["kv_rank"])),
+        "attn_heads": mix(lambda m, layer: (4.0 * n * m["heads"] * m["vdim"], 0.0)),
+        "mixer_out": mix(lambda m, layer: _product(n, W, m["heads"] * m["vdim"])),
+        "moe_ids": mlp(lambda f, layer: (4.0 * f["router"]["experts"] * W + 2.0 * n * W, 0.0)),
+        "moe_sorted": mlp(lambda f, layer: (12.0 * n * f["router"]["top"], 0.0)),
+        "moe_gate_up": mlp(lambda f, layer: (2.0 * (touched(f) * 2 * f["expert"]["ff"] * W + n * f["router"]["top"] * (W + 2 * f["expert"]["ff"])),
+                                             2.0 * n * f["router"]["top"] * 2 * f["expert"]["ff"] * W)),
+        "moe_act": mlp(lambda f, layer: (6.0 * n * f["router"]["top"] * f["expert"]["ff"], 0.0)),
+        "moe_expert_out": mlp(lambda f, layer: (2.0 * (touched(f) * f["expert"]["ff"] * W + n * f["router"]["top"] * (W + f["expert"]["ff"])),
+                                                2.0 * n * f["router"]["top"] * f["expert"]["ff"] * W)),
+        # (a routed layer's shared expert ends at the same taps as a dense feed-forward: its sizes are taken then)
+        "ffn_act": mlp(lambda f, layer: _product(n, 2 * (f["ff"] if f["kind"] == "dense" else f["shared"]["ff"]), W)),
+        "moe_shared_out": mlp(lambda f, layer: _product(n, W, f["shared"]["ff"])),
+        "ffn_out": mlp(lambda f, layer: _product(n, W, f["ff"]) if f["kind"] == "dense" else (2.0 * n * W * (f["router"]["top"] + 2), 0.0)),
+    }
+
+
+RESOLORN_PHASES = {"norm1": "add + norm", "latent_down": "down products (query latent, latent, gates)", "latent_q": "latent norms + cache write",
+                   "q_heads": "query up product", "q_latent": "queries into the latent's space (a product a head)",
+                   "attn_out": "attention over latents", "attn_values": "values out of the latent's space (a product a head)",
+                   "attn_heads": "head gates", "mixer_out": "output product", "moe_ids": "router", "moe_sorted": "grouping by expert",
+                   "moe_gate_up": "experts' gate/up products", "moe_act": "experts' activation", "moe_expert_out": "experts' down products",
+                   "ffn_act": "gate/up product + activation", "moe_shared_out": "down product", "ffn_out": None}
+
+
+def qwen3_costs(raw, starts, counts):
+    n, h, inter = sum(counts), raw["hidden_size"], raw["intermediate_size"]
+    nq, nkv, hd = raw["num_attention_heads"], raw["num_key_value_heads"], raw["head_dim"]
+    cached = sum(s + c for s, c in zip(starts, counts))
+    return {
+        "norm1": lambda layer: (n * h * 12.0, 0.0), "norm2": lambda layer: (n * h * 12.0, 0.0),
+        "qkv": lambda layer: _product(n, (nq + 2 * nkv) * hd, h),
+        "q_rot": lambda layer: (4.0 * n * (nq + 2 * nkv) * hd, 0.0),
+        "attn_out": lambda layer: (4.0 * cached * nkv * hd + 4.0 * n * nq * hd, 4.0 * _keys_seen(starts, counts, 0) * nq * hd),
+        "mixer_out": lambda layer: _product(n, h, nq * hd),
+        "ffn_act": lambda layer: _product(n, 2 * inter, h),
+        "ffn_out": lambda layer: _product(n, h, inter),
+    }
+
+
+QWEN3_PHASES = {"norm1": "add + norm", "norm2": "add + norm", "qkv": "q/k/v product", "q_rot": "norm + rotation + cache write",
+                "attn_out": "attention", "mixer_out": "output product", "ffn_act": "gate/up product + activation", "ffn_out": "down product"}
+
+
+def phase_table(engine, seqs, costs, names, layer_of, pk, reps, warmup):
+    """One forward pass over ``seqs`` captured with an event at every named tap, replayed ``reps`` times: rows of
+    (phase, calls, mean us, bytes, flops, fraction of its roofline), kernels in the order they run."""
+    import torch
+    from rust_mlx_b200.engine.batch import build_batch
+    e = engine
+    batch = build_batch(seqs, e.pools, e.device, e._status, e.vocab_size)
+    marks = []
+
+    def tap(name, tensor):
+        ev = torch.cuda.Event(enable_timing=True, external=True)
+        ev.record()
+        marks.append((name, getattr(e, "_run_index", 0), ev))
+
+    def step():
+        marks.clear()
+        tap("start", None)
+        tap("nothing", None)
+        e.forward(batch)
+    e.forward(batch)
+    torch.cuda.synchronize()
+    e._ctx.tap = tap
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+    finally:
+        e._ctx.tap = None
+    sums = {}
+    order = []
+    event_us = 0.0
+    for _ in range(warmup):
+        graph.replay()
+    for _ in range(reps):
+        graph.replay()
+        torch.cuda.synchronize()
+        last = marks[0][2]
+        for name, run, ev in marks[1:]:
+            if name == "nothing":
+                event_us += last.elapsed_time(ev) * 1e3
+                last = ev
+                continue
+            if name == "ffn_out" and names.get(name, name) is None:
+                # (the routed layer's last tap is its weighted sum; a dense layer's is its down product)
+                label = "weighted sum of the experts" if (layer_of(run).get("mlp") or {}).get("kind") == "moe" else "down product"
+            elif name not in names or name not in costs:
+                continue
+            else:
+                label = names[name]
+            b, f = costs[name](layer_of(run))
+            key = label
+            if key not in sums:
+                sums[key] = [0.0, 0, 0.0, 0.0]
+                order.append(key)
+            sums[key][0] += last.elapsed_time(ev) * 1e3
+            sums[key][1] += 1
+            sums[key][2] += b
+            sums[key][3] += f
+            last = ev
+    event_us /= reps
+    rows = []
+    for key in order:
+        us_total, calls, b, f = sums[key]
+        us = max(us_total / calls - event_us, 0.01)
+        b, f = b / calls, f / calls
+        floor_us = max(b / (pk["hbm_gbs"] * 1e3), f / (pk["bf16_tflops"] * 1e6))
+        rows.append({"phase": key, "calls_per_step": calls // reps, "us": round(us, 2), "mbytes": round(b / 1e6, 3), "gflop": round(f / 1e9, 3),
+                     "bound": "hbm" if b / (pk["hbm_gbs"] * 1e3) >= f / (pk["bf16_tflops"] * 1e6) else "tensor", "frac": round(floor_us / us, 4)})
+    return rows, event_us
+
+
+def family_resolorn(a):
+    """Decode (batch ``a.batch`` at context CONTEXT) and prefill (PREFILL_TOKENS tokens) of Resolorn layers beside Qwen3
+    layers of equal width, depth, head size and feed-forward width, with every phase against its roofline."""
+    import torch
+    from rust_mlx_b200.config import Qwen3Config, ResolornConfig
+    from rust_mlx_b200.engine import Engine
+    from rust_mlx_b200.engine.batch import SequenceInput
+    pk = peaks()
+    out = {"metric": "Resolorn beside Qwen3 at equal layer sizes: decode and prefill tok/s, phases against their rooflines", "impl": "ours",
+           "dtype": "bf16", "data": "synthetic", "n_gpus": 1, "batch": a.batch, "context": CONTEXT, "prefill_tokens": PREFILL_TOKENS,
+           "peaks": pk, "sizes": {}}
+    for size in (a.family_size.split(",") if a.family_size else sorted(FAMILY_SIZES)):
+        s = FAMILY_SIZES[size]
+        groups = max(1, a.family_layers // 4)
+        raw_r = resolorn_shape(groups=groups, **s)
+        raw_q = dict(QWEN3_8B, num_hidden_layers=4 * groups, hidden_size=s["width"], num_attention_heads=s["heads"],
+                     num_key_value_heads=max(1, s["heads"] // 4), head_dim=s["dim"], intermediate_size=s["ff"], vocab_size=s["vocab"],
+                     max_position_embeddings=2 * MAX_CONTEXT)
+        result = {}
+        for family, raw, cfg, costs_of, names in (("resolorn", raw_r, ResolornConfig.from_dict(raw_r), resolorn_costs, RESOLORN_PHASES),
+                                                  ("qwen3", raw_q, Qwen3Config.from_dict(raw_q), qwen3_costs, QWEN3_PHASES)):
+            cache_tokens = a.batch * (CONTEXT + 2 * PAGE + a.steps + a.warmup + 64) + 2 * PREFILL_TOKENS
+            engine = Engine(cfg, dtype="bfloat16", random_weights=True, seed=0, max_tokens=cache_tokens, page_size=PAGE,
+                            max_requests=a.batch + 4, tuning=a.policy)
+            for grp in engine.pools.paged_groups:
+                grp.k_pool.normal_(0, 1)
+                if grp.v_pool is not None:
+                    grp.v_pool.normal_(0, 1)
+            ms, launches, clock_info = time_decode(engine, a.batch, a.steps, a.warmup, ClockSampler())
+            pf_ms = time_prefill(engine, PREFILL_TOKENS)
+            layer_of = (lambda run, raw=raw: raw["layers"][run]) if family == "resolorn" else (lambda run: {})
+            # phases of a decode step and of a prompt
+            run = DecodeRun(engine, a.batch, CONTEXT)
+            try:
+                for r in run.rids:
+                    engine.pools.table.reserve(r, run.len + 1)
+                seqs = [SequenceInput(r, run.len, [run.ids[0][i]], [0]) for i, r in enumerate(run.rids)]
+                decode_rows, ev_us = phase_table(engine, seqs, costs_of(raw, [CONTEXT] * a.batch, [1] * a.batch), names, layer_of, pk,
+                                                 max(10, a.steps // 10), a.warmup)
+            finally:
+                run.close()
+            rid = 30_000
+            engine.pools.open(rid)
+            engine.pools.table.reserve(rid, PREFILL_TOKENS)
+            try:
+                g = torch.Generator().manual_seed(2)
+                ids = torch.randint(0, engine.vocab_size, (PREFILL_TOKENS,), generator=g).tolist()
+                prefill_rows, _ = phase_table(engine, [SequenceInput(rid, 0, ids, [PREFILL_TOKENS - 1])],
+                                              costs_of(raw, [0], [PREFILL_TOKENS]), names, layer_of, pk, 5, 2)
+            finally:
+                engine.pools.table.close(rid)
+            engine.check_status()
+            result[family] = {"decode_tok_per_s": round(a.batch * 1000.0 / ms, 1), "decode_ms_per_step": round(ms, 4),
+                              "prefill_tok_per_s": round(PREFILL_TOKENS / (pf_ms * 1e-3), 1), "prefill_ms": round(pf_ms, 3),
+                              "layers": 4 * groups, "launches_per_decode_step": launches // a.steps, "clocks": clock_info,
+                              "decode_phases": decode_rows, "prefill_phases": prefill_rows, "event_us": round(ev_us, 2)}
+            for mode, rows in (("decode", decode_rows), ("prefill", prefill_rows)):
+                print(f"-- {family} {size} {mode}: {result[family][mode + '_tok_per_s' if mode == 'decode' else 'prefill_tok_per_s']} tok/s", file=sys.stderr)
+                for r_ in rows:
+                    print(f"  {r_['phase']:52s} x{r_['calls_per_step']:<3d} {r_['us']:10.2f} us {r_['mbytes']:10.2f} MB {r_['gflop']:10.2f} GF "
+                          f"{r_['bound']:7s} {r_['frac']:7.3f}", file=sys.stderr)
+            del engine
+            torch.cuda.empty_cache()
+        out["sizes"][size] = {"shape": s, **result}
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     global CONTEXT, MAX_CONTEXT
     ap = argparse.ArgumentParser()
@@ -380,6 +645,12 @@ def main():
     ap.add_argument("--continuous", action="store_true",
                     help="instead: 64 requests with prompts of 128..3072 random ids, 256 tokens each, through the "
                          "scheduler with chunked prefill of 512 (continuous batching); prints its own JSON line")
+    ap.add_argument("--family", default="", choices=["", "resolorn"],
+                    help="instead: layers of this design at sizes of real models beside Qwen3 layers of equal width, depth, head "
+                         "size and feed-forward width: decode and prefill tok/s and every phase against its roofline; prints its own "
+                         "JSON line")
+    ap.add_argument("--family-size", default="", help="with --family: which sizes, comma separated (default: all of " + ", ".join(sorted(FAMILY_SIZES)) + ")")
+    ap.add_argument("--family-layers", type=int, default=4, help="with --family: layers (a multiple of four)")
     ap.add_argument("--policy", default="auto", choices=["auto", "measured", "all", "none"],
                     help="which products of few rows take the tcgen05 kernel (auto: time both when the engine starts)")
     a = ap.parse_args()
@@ -398,6 +669,9 @@ def main():
     from rust_mlx_b200.engine import Engine
 
     CONTEXT = a.context
+    if a.family:
+        MAX_CONTEXT = max(MAX_CONTEXT, 2 * CONTEXT)
+        return family_resolorn(a)
     base = SHAPES[a.shape]
     if a.shape != "qwen3-8b" and a.layers == QWEN3_8B["num_hidden_layers"]:
         a.layers = base["num_hidden_layers"]

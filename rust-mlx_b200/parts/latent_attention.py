@@ -87,6 +87,8 @@ class LatentAttentionMixer(Mixer):
         kv = r if self.own_latent else 0
         proj = ws.get("latent_down", (n, self.w_down.shape[0]), dt)
         ops.linear(x, self.w_down, proj, ws, batch.status)
+        if tap is not None:
+            tap("latent_down", proj)
         cq = ws.get("latent_q", (n, self.q_rank), dt)
         write = self.own_latent and not cache.read_only
         ops.latent_norms(proj, self.q_rank, kv, self.q_norm, self.kv_norm, self.eps, cq, cache.k_pool if write else None,
@@ -95,6 +97,8 @@ class LatentAttentionMixer(Mixer):
             tap("latent_q", cq)
         q = ws.get("q_heads", (n, H * self.dim), dt)
         ops.linear(cq, self.w_uq, q, ws, batch.status)
+        if tap is not None:
+            tap("q_heads", q)
         q_lat = ws.get("q_rot", (n, H * r), dt)
         ops.linear_heads(q.view(n, H, self.dim), self.w_uk_t, q_lat.view(n, H, r))
         if tap is not None:
@@ -106,6 +110,8 @@ class LatentAttentionMixer(Mixer):
             tap("attn_out", o_lat)
         o = ws.get("attn_heads", (n, H * self.vdim), dt)
         ops.linear_heads(o_lat.view(n, H, r), self.w_uv, o.view(n, H, self.vdim))
+        if tap is not None:
+            tap("attn_values", o)
         if self.gated:
             ops.gate_heads(o, proj[:, self.q_rank + kv:], H, self.vdim)
         if tap is not None:

@@ -60,20 +60,31 @@ class RoutedFeedForward(FeedForward):
         ids = ws.get("moe_ids", (n, top), torch.int32)
         weights = ws.get("moe_weights", (n, top), torch.float32)
         ops.moe_route(x, self.w_router, top, ids, weights)
+        tap = self.ctx.tap
+        if tap is not None:
+            tap("moe_ids", ids)
+            tap("moe_weights", weights)
         offsets = ws.get("moe_offsets", (e + 1,), torch.int32)
         pairs = ws.get("moe_sorted", (n * top,), torch.int32)
         where = ws.get("moe_where", (n * top,), torch.int32)
         ops.moe_sort(ids, e, offsets, pairs, where)
+        if tap is not None:
+            tap("moe_sorted", pairs)
         gu = ws.get("moe_gate_up", (n * top, 2 * self.inner), dt)
         ops.moe_gemm(x, self.w_gate_up, gu, offsets, sorted_pairs=pairs, top=top)
+        if tap is not None:
+            tap("moe_gate_up", gu)
         act = ws.get("moe_act", (n * top, self.inner), dt)
         ops.swiglu(gu, act, 0, self.activation)
+        if tap is not None:
+            tap("moe_act", act)
         y = ws.get("moe_expert_out", (n * top, self.width), dt)
         ops.moe_gemm(act, self.w_down, y, offsets)
+        if tap is not None:
+            tap("moe_expert_out", y)
         shared = self.shared.forward(x, batch, out_name="ffn_shared_out") if self.shared is not None else None
+        if tap is not None and shared is not None:
+            tap("moe_shared_out", shared)
         out = ws.get("ffn_out", (n, self.width), dt)
         ops.moe_combine(y, where, weights, shared, out)
-        if self.ctx.tap is not None:
-            self.ctx.tap("moe_ids", ids)
-            self.ctx.tap("moe_weights", weights)
         return out
