@@ -445,9 +445,10 @@ def resolorn_costs(raw, starts, counts):
         "mixer_out": mix(lambda m, layer: _product(n, W, m["heads"] * m["vdim"])),
         "moe_ids": mlp(lambda f, layer: (4.0 * f["router"]["experts"] * W + 2.0 * n * W, 0.0)),
         "moe_sorted": mlp(lambda f, layer: (12.0 * n * f["router"]["top"], 0.0)),
-        "moe_gate_up": mlp(lambda f, layer: (2.0 * (touched(f) * 2 * f["expert"]["ff"] * W + n * f["router"]["top"] * (W + 2 * f["expert"]["ff"])),
-                                             2.0 * n * f["router"]["top"] * 2 * f["expert"]["ff"] * W)),
-        "moe_act": mlp(lambda f, layer: (6.0 * n * f["router"]["top"] * f["expert"]["ff"], 0.0)),
+        "moe_rows": mlp(lambda f, layer: (4.0 * n * f["router"]["top"] * W, 0.0)),
+        # (gate/up product with act(gate) * up in its epilogue)
+        "moe_act": mlp(lambda f, layer: (2.0 * (touched(f) * 2 * f["expert"]["ff"] * W + n * f["router"]["top"] * (W + f["expert"]["ff"])),
+                                         2.0 * n * f["router"]["top"] * 2 * f["expert"]["ff"] * W)),
         "moe_expert_out": mlp(lambda f, layer: (2.0 * (touched(f) * f["expert"]["ff"] * W + n * f["router"]["top"] * (W + f["expert"]["ff"])),
                                                 2.0 * n * f["router"]["top"] * f["expert"]["ff"] * W)),
         # (a routed layer's shared expert ends at the same taps as a dense feed-forward: its sizes are taken then)
@@ -461,7 +462,8 @@ RESOLORN_PHASES = {"norm1": "add + norm", "latent_down": "down products (query l
                    "q_heads": "query up product", "q_latent": "queries into the latent's space (a product a head)",
                    "attn_out": "attention over latents", "attn_values": "values out of the latent's space (a product a head)",
                    "attn_heads": "head gates", "mixer_out": "output product", "moe_ids": "router", "moe_sorted": "grouping by expert",
-                   "moe_gate_up": "experts' gate/up products", "moe_act": "experts' activation", "moe_expert_out": "experts' down products",
+                   "moe_rows": "rows into the experts' order", "moe_act": "experts' gate/up products + activation",
+                   "moe_expert_out": "experts' down products",
                    "ffn_act": "gate/up product + activation", "moe_shared_out": "down product", "ffn_out": None}
 
 

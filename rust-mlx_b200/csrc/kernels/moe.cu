@@ -17,11 +17,73 @@
 namespace {
 
 // ---- router ---------------------------------------------------------------------------------------------------
-// One warp per row.  Logits in float from the row (in T) and the router's weight (float); ties go to the lower
-// expert.  ids [rows, top], weights [rows, top].
-template <typename T>
-__global__ void moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w, int width, int n_experts,
-                                 int top, int* __restrict__ ids, float* __restrict__ weights, int n_rows) {
+// Logits in float from the rows (in T) and the router's weight (float).  A warp takes one expert and up to ROWS rows,
+// so that a weight row is read once for all of them; a (row, expert) sum is formed lane by lane over groups of four
+// neighbouring numbers and then across the lanes, in an order that the width alone decides.
+__device__ __forceinline__ void route_load4(const float* p, float4& v) { v = *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ void route_load4(const __nv_bfloat16* p, float4& v) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    v = make_float4(a.x, a.y, b.x, b.y);
+}
+
+template <typename T, int ROWS>
+__global__ void __launch_bounds__(128) moe_logits_kernel(const T* __restrict__ x, const float* __restrict__ w, int width, int n_experts,
+                                                         int n_rows, float* __restrict__ logits) {
+    // a block of four warps takes one expert and up to ROWS rows; its 128 threads walk the width together (groups of
+    // four neighbouring numbers), each warp's lanes are added by the butterfly and the warps in their order
+    __shared__ float part[4][ROWS];
+    allow_dependents();
+    wait_for_prior_kernels();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.y;
+    const int row0 = blockIdx.x * ROWS;
+    const float* we = w + (size_t)e * width;
+    float acc[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) acc[r] = 0.f;
+    if ((width & 3) == 0) {
+#pragma unroll 2
+        for (int i = threadIdx.x * 4; i < width; i += 512) {
+            float4 wv;
+            route_load4(we + i, wv);
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+                if (row0 + r < n_rows) {
+                    float4 xv;
+                    route_load4(x + (size_t)(row0 + r) * width + i, xv);
+                    acc[r] = fmaf(xv.x, wv.x, acc[r]);
+                    acc[r] = fmaf(xv.y, wv.y, acc[r]);
+                    acc[r] = fmaf(xv.z, wv.z, acc[r]);
+                    acc[r] = fmaf(xv.w, wv.w, acc[r]);
+                }
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += 128) {
+            const float wv = we[i];
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r)
+                if (row0 + r < n_rows) acc[r] = fmaf(to_float(x[(size_t)(row0 + r) * width + i]), wv, acc[r]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        const float s = warp_sum(acc[r]);
+        if (lane == 0) part[warp][r] = s;
+    }
+    __syncthreads();
+    if (threadIdx.x < ROWS && row0 + threadIdx.x < n_rows) {
+        const int r = threadIdx.x;
+        logits[(size_t)(row0 + r) * n_experts + e] = ((part[0][r] + part[1][r]) + part[2][r]) + part[3][r];
+    }
+}
+
+// One warp per row: the `top` largest logits choose the experts (ties go to the lower expert); their weights are the
+// softmax over the chosen logits alone.  ids [rows, top], weights [rows, top].
+__global__ void moe_topk_kernel(const float* __restrict__ logits_in, int n_experts, int top, int* __restrict__ ids,
+                                float* __restrict__ weights, int n_rows) {
     extern __shared__ float logits_all[];
     allow_dependents();
     wait_for_prior_kernels();
@@ -29,14 +91,7 @@ __global__ void moe_route_kernel(const T* __restrict__ x, const float* __restric
     const int row = blockIdx.x * (blockDim.x >> 5) + warp;
     if (row >= n_rows) return;
     float* logits = logits_all + warp * n_experts;
-    const T* xr = x + (size_t)row * width;
-    for (int e = 0; e < n_experts; ++e) {
-        const float* we = w + (size_t)e * width;
-        float s = 0.f;
-        for (int i = lane; i < width; i += 32) s = fmaf(to_float(xr[i]), we[i], s);
-        s = warp_sum(s);
-        if (lane == 0) logits[e] = s;
-    }
+    for (int e = lane; e < n_experts; e += 32) logits[e] = logits_in[(size_t)row * n_experts + e];
     __syncwarp();
     float first = 0.f, total = 0.f, mine = 0.f;   // lane k keeps the k-th chosen logit (top <= 32)
     int mine_id = 0;
@@ -189,26 +244,75 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restric
     if (shared_out) acc += to_float(shared_out[idx]);
     out[idx] = from_float<T>(acc);
 }
+
+// bfloat16, eight columns a thread (16-byte accesses); width is a multiple of 8.  The same sums in the same order.
+__global__ void moe_combine8_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ where, const float* __restrict__ weights,
+                                    const __nv_bfloat16* __restrict__ shared_out, __nv_bfloat16* __restrict__ out, int top, int width,
+                                    size_t total8) {
+    allow_dependents();
+    wait_for_prior_kernels();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total8) return;
+    const int per_row = width >> 3;
+    const size_t row = idx / per_row;
+    const int col = (int)(idx - row * per_row) * 8;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int k = 0; k < top; ++k) {
+        const float wk = weights[row * top + k];
+        const uint4 raw = *reinterpret_cast<const uint4*>(y + (size_t)where[row * top + k] * width + col);
+        const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&words[j]));
+            acc[2 * j] = fmaf(wk, v.x, acc[2 * j]);
+            acc[2 * j + 1] = fmaf(wk, v.y, acc[2 * j + 1]);
+        }
+    }
+    if (shared_out) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(shared_out + row * width + col);
+        const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&words[j]));
+            acc[2 * j] += v.x;
+            acc[2 * j + 1] += v.y;
+        }
+    }
+    uint32_t packed[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 r = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        packed[j] = *reinterpret_cast<uint32_t*>(&r);
+    }
+    *reinterpret_cast<uint4*>(out + row * width + col) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+}
 }  // namespace
 
+// logits: [n_rows, n_experts] floats of scratch.
 RMX_API int rmx_moe_route(const void* x, const float* w_router, int n_rows, int width, int n_experts, int top, int* ids,
-                          float* weights, int dtype, void* stream) {
+                          float* weights, float* logits, int dtype, void* stream) {
     if (n_rows == 0) return 0;
     RMX_REQUIRE(n_rows > 0 && width > 0 && n_experts > 0 && top > 0 && top <= n_experts && top <= 32,
                 "moe_route: %d of %d experts (at most 32 a row)", top, n_experts);
     RMX_REQUIRE(n_experts <= 2048, "moe_route: more than 2048 experts");
-    const int warps = 4;
-    const size_t smem = (size_t)warps * n_experts * sizeof(float);
-    dim3 grid((n_rows + warps - 1) / warps);
+    RMX_REQUIRE(logits != nullptr, "moe_route: no room for the logits");
     cudaStream_t s = (cudaStream_t)stream;
+    constexpr int ROWS = 8;
+    const int warps = 4;
+    dim3 grid((n_rows + ROWS - 1) / ROWS, n_experts);
     if (dtype == RMX_F32)
-        RMX_CHECK_LAUNCHED(launch_dependent(moe_route_kernel<float>, grid, dim3(warps * 32), smem, s, (const float*)x, w_router, width,
-                                            n_experts, top, ids, weights, n_rows), "moe_route");
+        RMX_CHECK_LAUNCHED(launch_dependent(moe_logits_kernel<float, ROWS>, grid, dim3(warps * 32), 0, s, (const float*)x, w_router, width,
+                                            n_experts, n_rows, logits), "moe_route");
     else if (dtype == RMX_BF16)
-        RMX_CHECK_LAUNCHED(launch_dependent(moe_route_kernel<__nv_bfloat16>, grid, dim3(warps * 32), smem, s, (const __nv_bfloat16*)x,
-                                            w_router, width, n_experts, top, ids, weights, n_rows), "moe_route");
+        RMX_CHECK_LAUNCHED(launch_dependent(moe_logits_kernel<__nv_bfloat16, ROWS>, grid, dim3(warps * 32), 0, s, (const __nv_bfloat16*)x,
+                                            w_router, width, n_experts, n_rows, logits), "moe_route");
     else
         RMX_FAIL("moe_route: unknown dtype %d", dtype);
+    const int tw = 4;
+    RMX_CHECK_LAUNCHED(launch_dependent(moe_topk_kernel, dim3((n_rows + tw - 1) / tw), dim3(tw * 32), (size_t)tw * n_experts * sizeof(float), s,
+                                        (const float*)logits, n_experts, top, ids, weights, n_rows), "moe_route");
     return 0;
 }
 
@@ -258,7 +362,12 @@ RMX_API int rmx_moe_combine(const void* y, const int* where, const float* weight
     if (dtype == RMX_F32)
         RMX_CHECK_LAUNCHED(launch_dependent(moe_combine_kernel<float>, dim3(blocks), dim3(threads), 0, s, (const float*)y, where, weights,
                                             (const float*)shared_out, (float*)out, top, width, total), "moe_combine");
-    else if (dtype == RMX_BF16)
+    else if (dtype == RMX_BF16 && (width & 7) == 0 && ((uintptr_t)y & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)shared_out & 15) == 0) {
+        const size_t total8 = total / 8;
+        RMX_CHECK_LAUNCHED(launch_dependent(moe_combine8_kernel, dim3((unsigned)((total8 + threads - 1) / threads)), dim3(threads), 0, s,
+                                            (const __nv_bfloat16*)y, where, weights, (const __nv_bfloat16*)shared_out, (__nv_bfloat16*)out,
+                                            top, width, total8), "moe_combine");
+    } else if (dtype == RMX_BF16)
         RMX_CHECK_LAUNCHED(launch_dependent(moe_combine_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, s, (const __nv_bfloat16*)y,
                                             where, weights, (const __nv_bfloat16*)shared_out, (__nv_bfloat16*)out, top, width, total),
                            "moe_combine");

@@ -179,18 +179,23 @@ def gate_heads(o, gate, heads, vdim):
     _launched()
 
 
-def moe_route(x, w_router, top, ids_out, weights_out):
+def moe_route(x, w_router, top, ids_out, weights_out, logits=None):
     """Router of a mixture of experts: logits = x . w_router^T in float; per row the ``top`` largest choose the
-    experts (ids_out [rows, top] int32), weights_out = softmax over the chosen logits."""
+    experts (ids_out [rows, top] int32), weights_out = softmax over the chosen logits.  ``logits``: [rows, experts]
+    floats of scratch (made here if not given)."""
     lib = kernels_library()
     n, width = x.shape
     e = w_router.shape[0]
     if w_router.shape != (e, width) or ids_out.shape != (n, top) or weights_out.shape != (n, top):
         raise KernelError("moe_route: shapes do not fit")
+    if logits is None:
+        logits = torch.empty((n, e), dtype=torch.float32, device=x.device)
+    elif logits.shape != (n, e):
+        raise KernelError("moe_route: the logits' scratch must be [rows, experts]")
     check(lib.rmx_moe_route(_ptr(x, name="x"), _ptr(w_router, torch.float32, "w_router"), c_int(n), c_int(width), c_int(e),
                             c_int(top), _ptr(ids_out, torch.int32, "ids"), _ptr(weights_out, torch.float32, "weights"),
-                            c_int(dtype_code(x)), _stream()))
-    _launched()
+                            _ptr(logits, torch.float32, "logits"), c_int(dtype_code(x)), _stream()))
+    _launched(2)
 
 
 def moe_sort(ids, n_experts, offsets_out, sorted_out, where_out):
@@ -220,6 +225,39 @@ def moe_gemm(a, w, out, offsets, sorted_pairs=None, top=0):
                            c_int(top if sorted_pairs is not None else 0), _ptr(w, name="w"), _ptr(out, name="out"),
                            c_int(out.stride(0)), _ptr(offsets, torch.int32, "offsets"), c_int(e), c_int(total), c_int(n), c_int(k),
                            c_int(dtype_code(a)), _stream()))
+    _launched()
+
+
+def moe_gemm_tcgen05_supported(n: int, k: int) -> bool:
+    return bool(kernels_library().rmx_moe_gemm_tcgen05_supports(c_int(n), c_int(k)))
+
+
+def moe_gather(x, sorted_pairs, top, out):
+    """out[p] = x[sorted_pairs[p] // top]: the layer's rows in the order of the experts' runs (bfloat16, 16-byte copies)."""
+    lib = kernels_library()
+    total, width = out.shape
+    if x.shape[1] != width or sorted_pairs.numel() != total or x.dtype != out.dtype:
+        raise KernelError("moe_gather: shapes do not fit")
+    check(lib.rmx_moe_gather(_ptr(x, torch.bfloat16, "x"), _ptr(sorted_pairs, torch.int32, "sorted"), c_int(top),
+                             _ptr(out, torch.bfloat16, "out"), c_int(total), c_int(width), _stream()))
+    _launched()
+
+
+def moe_gemm_tcgen05(a, w, out, offsets, status, gated=False, activation="silu"):
+    """The experts' products on the tcgen05 tensor cores (bfloat16): out[p] = w[e] . a[p] for every place p of expert
+    e's run; ``a`` [places, K] in sorted order, ``w`` [experts, N, K].  ``gated``: an expert's rows come in blocks of 64
+    gate rows and their 64 up rows, and out [places, N / 2] = act(gate) * up."""
+    lib = kernels_library()
+    e, n, k = w.shape
+    total = a.shape[0]
+    if a.shape[1] != k or out.shape != (total, n // 2 if gated else n) or not w.is_contiguous() or a.stride(1) != 1:
+        raise KernelError(f"moe_gemm_tcgen05: {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"moe_gemm_tcgen05: unknown activation {activation!r}")
+    check(lib.rmx_moe_gemm_tcgen05(c_void_p(a.data_ptr()), c_int(a.stride(0)), _ptr(w, torch.bfloat16, "w"), _ptr(out, torch.bfloat16, "out"),
+                                   c_int(out.stride(0)), _ptr(offsets, torch.int32, "offsets"), c_int(e), c_int(total), c_int(n),
+                                   c_int(k), c_int(1 if gated else 0), c_int(ACTIVATIONS[activation]), _ptr(status, torch.int32, "status"),
+                                   _stream()))
     _launched()
 
 
@@ -636,6 +674,7 @@ class Kernels:
         self.fused_decode_rope = True       # a decoding attention norms and rotates its own token while it waits for keys
         self.fused_swiglu = True            # the gate/up product of few rows forms silu(gate) * up in its epilogue
         self.use_tcgen05_attention = True   # prompt portions at head size 128 run on the tcgen05 tensor cores
+        self.use_tcgen05_experts = True     # a routed feed-forward's products run on the tcgen05 tensor cores (bfloat16)
         self._splits_memo = {}
 
     def __getattr__(self, name):

@@ -5,10 +5,13 @@
     y = sum over e in E(x) of weight_e * expert_e(x)  (+ shared(x))
     expert(x) = down(act(gate x) * (up x)), no biases
 
-The experts' weights are kept stacked, [experts, 2 * inner, width] (gate rows, then up rows) and
-[experts, width, inner].  A step sorts its (row, choice) pairs by expert on the device and the experts'
-products run over their runs of rows (``csrc/kernels/moe.cu``); nothing waits for the host, so decode
-steps can be captured in graphs.  The shared expert is a gated feed-forward like any other.
+The experts' weights are kept stacked, [experts, 2 * inner, width] and [experts, width, inner]; an expert's gate and
+up rows come in blocks of 64 gate rows each followed by their 64 up rows (plain concatenation when the inner size
+is no multiple of 64), as the dense feed-forward keeps them.  A step sorts its (row, choice) pairs by expert on the
+device and the experts' products run over their runs of rows: in bfloat16 on the tcgen05 tensor cores
+(``csrc/kernels/moe_tcgen05.cu``; with blocks of 64 the gate/up product forms act(gate) * up in its epilogue), in
+float32 on the FMA units with every sum in ascending k (``csrc/kernels/moe.cu``).  Nothing waits for the host, so
+decode steps can be captured in graphs.  The shared expert is a gated feed-forward like any other.
 """
 from __future__ import annotations
 
@@ -48,8 +51,14 @@ class RoutedFeedForward(FeedForward):
         super().bind(tensors, ctx)
         self.w_router = tensors[self.router].contiguous()
         gu, down = [], []
+        self.block = 64 if self.inner % 64 == 0 else 0
         for gate, up, d in self.expert_names:
-            gu.append(torch.cat([tensors.pop(gate), tensors.pop(up)], dim=0))
+            g, u = tensors.pop(gate), tensors.pop(up)
+            if self.block:
+                g, u = g.view(self.inner // 64, 64, self.width), u.view(self.inner // 64, 64, self.width)
+                gu.append(torch.stack([g, u], dim=1).reshape(2 * self.inner, self.width))
+            else:
+                gu.append(torch.cat([g, u], dim=0))
             down.append(tensors.pop(d))
         self.w_gate_up = torch.stack(gu).contiguous()      # [experts, 2 * inner, width]
         self.w_down = torch.stack(down).contiguous()       # [experts, width, inner]
@@ -59,7 +68,7 @@ class RoutedFeedForward(FeedForward):
         n, top, e = x.shape[0], self.top, self.n_experts
         ids = ws.get("moe_ids", (n, top), torch.int32)
         weights = ws.get("moe_weights", (n, top), torch.float32)
-        ops.moe_route(x, self.w_router, top, ids, weights)
+        ops.moe_route(x, self.w_router, top, ids, weights, ws.get("moe_logits", (n, e), torch.float32))
         tap = self.ctx.tap
         if tap is not None:
             tap("moe_ids", ids)
@@ -70,16 +79,36 @@ class RoutedFeedForward(FeedForward):
         ops.moe_sort(ids, e, offsets, pairs, where)
         if tap is not None:
             tap("moe_sorted", pairs)
-        gu = ws.get("moe_gate_up", (n * top, 2 * self.inner), dt)
-        ops.moe_gemm(x, self.w_gate_up, gu, offsets, sorted_pairs=pairs, top=top)
-        if tap is not None:
-            tap("moe_gate_up", gu)
         act = ws.get("moe_act", (n * top, self.inner), dt)
-        ops.swiglu(gu, act, 0, self.activation)
-        if tap is not None:
-            tap("moe_act", act)
         y = ws.get("moe_expert_out", (n * top, self.width), dt)
-        ops.moe_gemm(act, self.w_down, y, offsets)
+        tensor_cores = (dt == torch.bfloat16 and ops.use_tcgen05_experts and batch is not None
+                        and ops.moe_gemm_tcgen05_supported(2 * self.inner, self.width)
+                        and ops.moe_gemm_tcgen05_supported(self.width, self.inner))
+        if tensor_cores:
+            rows = ws.get("moe_rows", (n * top, self.width), dt)
+            ops.moe_gather(x, pairs, top, rows)
+            if tap is not None:
+                tap("moe_rows", rows)
+            if self.block:
+                ops.moe_gemm_tcgen05(rows, self.w_gate_up, act, offsets, batch.status, gated=True, activation=self.activation)
+            else:
+                gu = ws.get("moe_gate_up", (n * top, 2 * self.inner), dt)
+                ops.moe_gemm_tcgen05(rows, self.w_gate_up, gu, offsets, batch.status)
+                if tap is not None:
+                    tap("moe_gate_up", gu)
+                ops.swiglu(gu, act, 0, self.activation)
+            if tap is not None:
+                tap("moe_act", act)
+            ops.moe_gemm_tcgen05(act, self.w_down, y, offsets, batch.status)
+        else:
+            gu = ws.get("moe_gate_up", (n * top, 2 * self.inner), dt)
+            ops.moe_gemm(x, self.w_gate_up, gu, offsets, sorted_pairs=pairs, top=top)
+            if tap is not None:
+                tap("moe_gate_up", gu)
+            ops.swiglu(gu, act, self.block, self.activation)
+            if tap is not None:
+                tap("moe_act", act)
+            ops.moe_gemm(act, self.w_down, y, offsets)
         if tap is not None:
             tap("moe_expert_out", y)
         shared = self.shared.forward(x, batch, out_name="ffn_shared_out") if self.shared is not None else None

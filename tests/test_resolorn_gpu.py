@@ -138,6 +138,70 @@ def test_router_sort_products_and_weighted_sum(rows, width, experts, top):
         assert ((out.double() - (want_out - shared.double())).abs() <= tol * (1 + want_out.abs())).all()
 
 
+@pytest.mark.parametrize("rows, top, experts, n_out, k", [(3, 2, 8, 72, 64), (64, 4, 6, 128, 200), (700, 2, 3, 320, 96),
+                                                         (40, 1, 5, 200, 136), (2048, 2, 4, 256, 512)])
+def test_experts_products_on_the_tensor_cores(rows, top, experts, n_out, k):
+    """Few, some and many rows an expert (tiles of 16, 64 and 128 rows), experts without rows, weight rows that are
+    no multiple of 128, K with a ragged last block of 64; plain and with the gated epilogue."""
+    from rust_mlx_b200.kernels import ops
+    torch.manual_seed(rows + k)
+    x = torch.randn(rows, k, device=DEV).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(experts, device=DEV)[:top] for _ in range(rows)]).to(torch.int32)
+    if top == 1 and experts > 2:
+        ids[ids == 1] = 0                                         # expert 1 gets no rows at all
+    offsets = torch.empty(experts + 1, dtype=torch.int32, device=DEV)
+    pairs = torch.empty(rows * top, dtype=torch.int32, device=DEV)
+    where = torch.empty(rows * top, dtype=torch.int32, device=DEV)
+    ops.moe_sort(ids, experts, offsets, pairs, where)
+    xs = torch.empty(rows * top, k, dtype=torch.bfloat16, device=DEV)
+    ops.moe_gather(x, pairs, top, xs)
+    assert torch.equal(xs, x[pairs.long() // top])
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    which = ids.flatten().long()[pairs.long()]
+    w = (torch.randn(experts, n_out, k, device=DEV) * 0.1).to(torch.bfloat16)
+    y = torch.full((rows * top, n_out), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.moe_gemm_tcgen05(xs, w, y, offsets, status)
+    assert status.item() == 0
+    want = torch.stack([w[e].double() @ xs[i].double() for i, e in enumerate(which.tolist())]) if rows * top <= 256 else \
+        torch.cat([xs[offsets[e]:offsets[e + 1]].double() @ w[e].double().T for e in range(experts)])
+    assert ((y.double() - want).abs() <= 2e-2 * (1 + want.abs())).all()
+    if n_out % 128 == 0:
+        for activation, f in (("silu", plain.silu), ("gelu_tanh", plain.gelu_tanh)):
+            act = torch.full((rows * top, n_out // 2), float("nan"), dtype=torch.bfloat16, device=DEV)
+            ops.moe_gemm_tcgen05(xs, w, act, offsets, status, gated=True, activation=activation)
+            blocks = want.view(rows * top, n_out // 128, 2, 64)
+            want_act = (f(blocks[:, :, 0]) * blocks[:, :, 1]).reshape(rows * top, n_out // 2)
+            assert status.item() == 0
+            assert ((act.double() - want_act).abs() <= 2e-2 * (1 + want_act.abs())).all()
+
+
+def test_routed_part_in_bfloat16_on_the_tensor_cores_against_the_fma_kernels():
+    from rust_mlx_b200.kernels import ops
+    from rust_mlx_b200.parts.feedforward import SwiGLUFeedForward
+    from rust_mlx_b200.parts.routed import RoutedFeedForward
+
+    class Batch:
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+
+    for inner in (64, 40):            # with and without blocks of 64 (the gated epilogue)
+        ff = RoutedFeedForward("m", 96, inner, 6, 2, shared=SwiGLUFeedForward("m.shared", 96, 32, names=("gate", "up", "down")))
+        w = bind(ff, seed=inner, dtype=torch.bfloat16, scale={".router": 50.0, ".gate": 10.0, ".up": 10.0, ".down": 10.0})
+        for rows in (5, 300):
+            x = torch.randn(rows, 96, device=DEV).to(torch.bfloat16)
+            got = ff.forward(x, Batch()).clone()
+            ff.ctx.ops.use_tcgen05_experts = False
+            try:
+                other = ff.forward(x, Batch()).clone()
+            finally:
+                ff.ctx.ops.use_tcgen05_experts = True
+            mlp = {"router": {"experts": 6, "top": 2}, "shared": {"ff": 32}}
+            want = plain.routed_experts(x.double().cpu(), w, "m", mlp, bf16=True)
+            for y in (got, other):
+                err = tr.row_error(y.cpu(), want)
+                assert (err > 0.05).sum().item() <= 0.02 * rows, err.max().item()
+            assert Batch.status.item() == 0
+
+
 def test_products_of_heads_with_their_own_matrices():
     from rust_mlx_b200.kernels import ops
     rows, heads, k, n = 13, 3, 24, 40
