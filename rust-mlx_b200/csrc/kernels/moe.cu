@@ -28,55 +28,74 @@ __device__ __forceinline__ void route_load4(const __nv_bfloat16* p, float4& v) {
     v = make_float4(a.x, a.y, b.x, b.y);
 }
 
-template <typename T, int ROWS>
+template <typename T, int ROWS, int EXP>
 __global__ void __launch_bounds__(128) moe_logits_kernel(const T* __restrict__ x, const float* __restrict__ w, int width, int n_experts,
                                                          int n_rows, float* __restrict__ logits) {
-    // a block of four warps takes one expert and up to ROWS rows; its 128 threads walk the width together (groups of
-    // four neighbouring numbers), each warp's lanes are added by the butterfly and the warps in their order
-    __shared__ float part[4][ROWS];
+    // a block of four warps takes EXP experts and up to ROWS rows, so that a row is fetched once for EXP experts and a
+    // weight row once for ROWS rows; its 128 threads walk the width together (groups of four neighbouring numbers), each
+    // warp's lanes are added by the butterfly and the warps in their order: the order of a (row, expert) sum follows the
+    // width alone
+    __shared__ float part[4][ROWS][EXP];
     allow_dependents();
     wait_for_prior_kernels();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int e = blockIdx.y;
+    const int e0 = blockIdx.y * EXP;
     const int row0 = blockIdx.x * ROWS;
-    const float* we = w + (size_t)e * width;
-    float acc[ROWS];
+    float acc[ROWS][EXP];
 #pragma unroll
-    for (int r = 0; r < ROWS; ++r) acc[r] = 0.f;
+    for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+        for (int j = 0; j < EXP; ++j) acc[r][j] = 0.f;
     if ((width & 3) == 0) {
-#pragma unroll 2
         for (int i = threadIdx.x * 4; i < width; i += 512) {
-            float4 wv;
-            route_load4(we + i, wv);
+            float4 wv[EXP];
+#pragma unroll
+            for (int j = 0; j < EXP; ++j) {
+                wv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (e0 + j < n_experts) route_load4(w + (size_t)(e0 + j) * width + i, wv[j]);
+            }
 #pragma unroll
             for (int r = 0; r < ROWS; ++r) {
                 if (row0 + r < n_rows) {
                     float4 xv;
                     route_load4(x + (size_t)(row0 + r) * width + i, xv);
-                    acc[r] = fmaf(xv.x, wv.x, acc[r]);
-                    acc[r] = fmaf(xv.y, wv.y, acc[r]);
-                    acc[r] = fmaf(xv.z, wv.z, acc[r]);
-                    acc[r] = fmaf(xv.w, wv.w, acc[r]);
+#pragma unroll
+                    for (int j = 0; j < EXP; ++j) {
+                        acc[r][j] = fmaf(xv.x, wv[j].x, acc[r][j]);
+                        acc[r][j] = fmaf(xv.y, wv[j].y, acc[r][j]);
+                        acc[r][j] = fmaf(xv.z, wv[j].z, acc[r][j]);
+                        acc[r][j] = fmaf(xv.w, wv[j].w, acc[r][j]);
+                    }
                 }
             }
         }
     } else {
         for (int i = threadIdx.x; i < width; i += 128) {
-            const float wv = we[i];
+            float wv[EXP];
 #pragma unroll
-            for (int r = 0; r < ROWS; ++r)
-                if (row0 + r < n_rows) acc[r] = fmaf(to_float(x[(size_t)(row0 + r) * width + i]), wv, acc[r]);
+            for (int j = 0; j < EXP; ++j) wv[j] = e0 + j < n_experts ? w[(size_t)(e0 + j) * width + i] : 0.f;
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) {
+                if (row0 + r < n_rows) {
+                    const float xv = to_float(x[(size_t)(row0 + r) * width + i]);
+#pragma unroll
+                    for (int j = 0; j < EXP; ++j) acc[r][j] = fmaf(xv, wv[j], acc[r][j]);
+                }
+            }
         }
     }
 #pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-        const float s = warp_sum(acc[r]);
-        if (lane == 0) part[warp][r] = s;
-    }
+    for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+        for (int j = 0; j < EXP; ++j) {
+            const float s = warp_sum(acc[r][j]);
+            if (lane == 0) part[warp][r][j] = s;
+        }
     __syncthreads();
-    if (threadIdx.x < ROWS && row0 + threadIdx.x < n_rows) {
-        const int r = threadIdx.x;
-        logits[(size_t)(row0 + r) * n_experts + e] = ((part[0][r] + part[1][r]) + part[2][r]) + part[3][r];
+    if (threadIdx.x < ROWS * EXP) {
+        const int r = threadIdx.x / EXP, j = threadIdx.x % EXP;
+        if (row0 + r < n_rows && e0 + j < n_experts)
+            logits[(size_t)(row0 + r) * n_experts + e0 + j] = ((part[0][r][j] + part[1][r][j]) + part[2][r][j]) + part[3][r][j];
     }
 }
 
@@ -300,13 +319,14 @@ RMX_API int rmx_moe_route(const void* x, const float* w_router, int n_rows, int 
     RMX_REQUIRE(logits != nullptr, "moe_route: no room for the logits");
     cudaStream_t s = (cudaStream_t)stream;
     constexpr int ROWS = 8;
+    constexpr int EXP = 4;
     const int warps = 4;
-    dim3 grid((n_rows + ROWS - 1) / ROWS, n_experts);
+    dim3 grid((n_rows + ROWS - 1) / ROWS, (n_experts + EXP - 1) / EXP);
     if (dtype == RMX_F32)
-        RMX_CHECK_LAUNCHED(launch_dependent(moe_logits_kernel<float, ROWS>, grid, dim3(warps * 32), 0, s, (const float*)x, w_router, width,
+        RMX_CHECK_LAUNCHED(launch_dependent(moe_logits_kernel<float, ROWS, EXP>, grid, dim3(warps * 32), 0, s, (const float*)x, w_router, width,
                                             n_experts, n_rows, logits), "moe_route");
     else if (dtype == RMX_BF16)
-        RMX_CHECK_LAUNCHED(launch_dependent(moe_logits_kernel<__nv_bfloat16, ROWS>, grid, dim3(warps * 32), 0, s, (const __nv_bfloat16*)x,
+        RMX_CHECK_LAUNCHED(launch_dependent(moe_logits_kernel<__nv_bfloat16, ROWS, EXP>, grid, dim3(warps * 32), 0, s, (const __nv_bfloat16*)x,
                                             w_router, width, n_experts, n_rows, logits), "moe_route");
     else
         RMX_FAIL("moe_route: unknown dtype %d", dtype);

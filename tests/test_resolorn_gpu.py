@@ -175,6 +175,40 @@ def test_experts_products_on_the_tensor_cores(rows, top, experts, n_out, k):
             assert ((act.double() - want_act).abs() <= 2e-2 * (1 + want_act.abs())).all()
 
 
+def test_experts_products_tile_arrangements_agree():
+    """The arrangements kept for comparisons (two weight tiles a block; tiles of 256 rows) against the default."""
+    import ctypes
+    from rust_mlx_b200.kernels import ops
+    from rust_mlx_b200.kernels.library import kernels_library
+    lib = kernels_library()
+    torch.manual_seed(5)
+    experts, n_out, k, rows, top = 3, 384, 200, 900, 2
+    x = torch.randn(rows * top, k, device=DEV).to(torch.bfloat16)
+    ids = torch.randint(0, experts, (rows * top, 1), device=DEV, dtype=torch.int32)
+    offsets = torch.empty(experts + 1, dtype=torch.int32, device=DEV)
+    pairs = torch.empty(rows * top, dtype=torch.int32, device=DEV)
+    where = torch.empty(rows * top, dtype=torch.int32, device=DEV)
+    ops.moe_sort(ids, experts, offsets, pairs, where)
+    w = (torch.randn(experts, n_out, k, device=DEV) * 0.1).to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    outs = {}
+    try:
+        for variant in (0, 1, 2):
+            lib.rmx_moe_set_tile_variant(ctypes.c_int(variant))
+            for gated in (False, True):
+                y = torch.full((rows * top, n_out // 2 if gated else n_out), float("nan"), dtype=torch.bfloat16, device=DEV)
+                ops.moe_gemm_tcgen05(x, w, y, offsets, status, gated=gated)
+                outs[(variant, gated)] = y
+    finally:
+        lib.rmx_moe_set_tile_variant(ctypes.c_int(0))
+    assert status.item() == 0
+    for gated in (False, True):
+        assert not torch.isnan(outs[(0, gated)].float()).any()
+        for variant in (1, 2):
+            a, b = outs[(0, gated)].double(), outs[(variant, gated)].double()
+            assert ((a - b).abs() <= 1e-2 * (1 + a.abs())).all()
+
+
 def test_routed_part_in_bfloat16_on_the_tensor_cores_against_the_fma_kernels():
     from rust_mlx_b200.kernels import ops
     from rust_mlx_b200.parts.feedforward import SwiGLUFeedForward
