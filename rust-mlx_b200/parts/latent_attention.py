@@ -40,8 +40,15 @@ class LatentAttentionMixer(Mixer):
     def cache_spec(self):
         return CacheSpec("paged", kv_heads=1, head_dim=self.kv_rank, window=self.cache_window, values=False)
 
+    def heads_a_call(self) -> int:
+        """How many heads one attention launch takes: all of them share the one latent "kv head", and the kernels take
+        groups of up to 16 query heads (the tensor-core kernels by their tiles; the FMA kernel runs a warp a head and
+        has registers for 16 of them in a block).  More heads go in several launches over the same latents."""
+        return min(self.heads, 16)
+
     def graph_key(self, shape):
-        return (self.ctx.ops.decode_attention_splits(shape.n_seqs, 1, self.kv_rank, self.heads, shape.max_seq_len, self.ctx.dtype),)
+        return (self.ctx.ops.decode_attention_splits(shape.n_seqs, 1, self.kv_rank, self.heads_a_call(), shape.max_seq_len,
+                                                     self.ctx.dtype),)
 
     def param_specs(self):
         p = self.prefix
@@ -104,8 +111,19 @@ class LatentAttentionMixer(Mixer):
         if tap is not None:
             tap("q_latent", q_lat)
         o_lat = ws.get("attn_out", (n, H * r), dt)
-        ops.attention(q_lat, cache.k_pool, cache.k_pool, batch, cache.block_table, cache.page_size, o_lat, H, 1, r,
-                      self.window, self.scale, ws)
+        step = self.heads_a_call()
+        if step >= H:
+            ops.attention(q_lat, cache.k_pool, cache.k_pool, batch, cache.block_table, cache.page_size, o_lat, H, 1, r,
+                          self.window, self.scale, ws)
+        else:
+            for h0 in range(0, H, step):
+                hc = min(step, H - h0)
+                q_part = ws.get("q_rot_part", (n, hc * r), dt)
+                o_part = ws.get("attn_out_part", (n, hc * r), dt)
+                q_part.view(n, hc, r).copy_(q_lat.view(n, H, r)[:, h0:h0 + hc])
+                ops.attention(q_part, cache.k_pool, cache.k_pool, batch, cache.block_table, cache.page_size, o_part, hc, 1, r,
+                              self.window, self.scale, ws)
+                o_lat.view(n, H, r)[:, h0:h0 + hc].copy_(o_part.view(n, hc, r))
         if tap is not None:
             tap("attn_out", o_lat)
         o = ws.get("attn_heads", (n, H * self.vdim), dt)

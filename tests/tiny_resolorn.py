@@ -53,7 +53,14 @@ R3 = {"architecture": "Resolorn", "vocab": 320, "width": 128, "max_positions": 1
                  _layer(_mixer(8, 16, 32, 48, 128, kv_from=0), _moe(64, 4, 2, shared=64))]}
 PAGE_R3 = 64
 
-CONFIGS = {"R1": (R1, PAGE_R1), "R2": (R2, PAGE_R2), "R3": (R3, PAGE_R3)}
+# R4: more heads than an attention launch takes (20 over a latent of 64: 16 + 4; 40 over one of 24: 16 + 16 + 8), top 1 of 1
+R4 = {"architecture": "Resolorn", "vocab": 150, "width": 80, "max_positions": 256, "norm": {"eps": 1e-6},
+      "residual_mult": 0.4,
+      "layers": [_layer(_mixer(20, 8, 8, 24, 64, window=40), _moe(16, 1, 1)),
+                 _layer(_mixer(40, 4, 4, 16, 24), {"kind": "dense", "ff": 56})]}
+PAGE_R4 = 16
+
+CONFIGS = {"R1": (R1, PAGE_R1), "R2": (R2, PAGE_R2), "R3": (R3, PAGE_R3), "R4": (R4, PAGE_R4)}
 
 
 def make_folder(tmp_path, raw: dict, seed: int = 0, sharp: float = 8.0, out_boost: float = 20.0) -> str:
