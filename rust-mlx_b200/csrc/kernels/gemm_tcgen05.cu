@@ -39,8 +39,17 @@ struct GemmParams {
     int no_loads;            // test only: the producer issues no copies, so that every wait for a tile runs out
     int dependent;           // launched as a programmatic dependent: wait for the grid before before reading A
     int epilogue;            // 0: C = product.  1: the tile's rows are 64 gate rows then their 64 up rows;
-                             //    C[M, N / 2] = silu(gate) * up, formed in float and rounded once.
+                             //    C[M, N / 2] = act(gate) * up, formed in float and rounded once.
+    int act;                 // the gated epilogue's activation: 0 silu, 1 the tanh form of GELU
 };
+
+__device__ __forceinline__ float gate_activation(float g, int act) {
+    if (act == 1) {
+        const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+        return 0.5f * g * (1.f + tanhf(inner));
+    }
+    return g / (1.f + expf(-g));
+}
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -201,7 +210,7 @@ __global__ void __launch_bounds__(THREADS) gemm_swapab_kernel(const __grid_const
                 __syncthreads();
                 const int col = tile * 64 + tid;
                 if (tid < 64 && col < p.N / 2) {
-                    const float v = sum / (1.f + expf(-sum)) * ex[tid];
+                    const float v = gate_activation(sum, p.act) * ex[tid];
                     if (p.out_float) reinterpret_cast<float*>(p.c)[(size_t)t * p.ldc + col] = v;
                     else reinterpret_cast<__nv_bfloat16*>(p.c)[(size_t)t * p.ldc + col] = __float2bfloat16_rn(v);
                 }
@@ -274,7 +283,7 @@ __global__ void __launch_bounds__(THREADS) gemm_swapab_kernel(const __grid_const
             for (int t = 0; t < MPAD; ++t) {
                 if (t < p.M) {
                     const float g = acc[t], u = ex[t * 64 + tid];
-                    const float v = g / (1.f + expf(-g)) * u;
+                    const float v = gate_activation(g, p.act) * u;
                     if (p.out_float) reinterpret_cast<float*>(p.c)[(size_t)t * p.ldc + col] = v;
                     else reinterpret_cast<__nv_bfloat16*>(p.c)[(size_t)t * p.ldc + col] = __float2bfloat16_rn(v);
                 }
@@ -440,7 +449,7 @@ int gemm_tcgen05_run(const void* A, const void* W, void* C, int M, int N, int K,
     const bool fits = reduce_bytes <= (size_t)stages * (TILE_N * TILE_K * 2 + mpad * TILE_K * 2);
     const bool cluster = (flags & 1) && splits >= 2 && splits <= 8 && fits;
     const bool dependent = (flags & 2) != 0;
-    const int epilogue = (flags & 4) ? 1 : 0;   // flags: 4 = SwiGLU over blocks of 64 gate rows and 64 up rows
+    const int epilogue = (flags & 4) ? 1 : 0;   // flags: 4 = act(gate) * up over blocks of 64 gate rows and 64 up rows; 8 = act is GELU (tanh form)
     RMX_REQUIRE(epilogue != 1 || N % 128 == 0, "gemm_tcgen05: the SwiGLU epilogue needs N to be a multiple of 128, got %d", N);
     RMX_REQUIRE(splits == 1 || cluster || (partial && counters), "gemm_tcgen05: split-K needs scratch");
     CUtensorMap mw, ma;
@@ -449,7 +458,7 @@ int gemm_tcgen05_run(const void* A, const void* W, void* C, int M, int N, int K,
     GemmParams p;
     p.c = C; p.partial = partial; p.counters = counters; p.status = status;
     p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.splits = splits; p.k_blocks = k_blocks; p.out_float = out_float;
-    p.dependent = 0; p.epilogue = epilogue; p.spin_limit = spin_limit; p.no_loads = no_loads;
+    p.dependent = 0; p.epilogue = epilogue; p.act = (flags & 8) ? 1 : 0; p.spin_limit = spin_limit; p.no_loads = no_loads;
     // stages sized so that two blocks fit an SM: more blocks in flight smooth the last wave
     if (mpad == 16) return launch<16, 6>(mw, ma, p, n_tiles, s, cluster, dependent);
     if (mpad == 32) return launch<32, 5>(mw, ma, p, n_tiles, s, cluster, dependent);
@@ -561,7 +570,7 @@ RMX_API int rmx_gemm_tcgen05_static(const void* A, const void* W, void* C, int M
     GemmParams p;
     p.c = C; p.partial = scratch.partial; p.counters = scratch.counters; p.status = scratch.status;
     p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.splits = splits; p.k_blocks = k_blocks; p.out_float = out_float;
-    p.dependent = 0; p.epilogue = 0; p.spin_limit = SPIN_LIMIT; p.no_loads = 0;
+    p.dependent = 0; p.epilogue = 0; p.act = 0; p.spin_limit = SPIN_LIMIT; p.no_loads = 0;
     if (mpad == 16) return launch<16, 5>(mw, ma, p, n_tiles, s);
     if (mpad == 32) return launch<32, 5>(mw, ma, p, n_tiles, s);
     return launch<64, 4>(mw, ma, p, n_tiles, s);

@@ -520,7 +520,8 @@ def tcgen05_splits(m: int, n: int, k: int) -> int:
     return max(1, min(splits, 8, k_blocks // 4))
 
 
-def gemm_tcgen05(a, w, out, workspace=None, status=None, splits=None, cluster=True, dependent=False, swiglu=False):
+def gemm_tcgen05(a, w, out, workspace=None, status=None, splits=None, cluster=True, dependent=False, swiglu=False,
+                 activation="silu"):
     """out[M, N] = a[M, K] . w[N, K]^T for M <= 64 on the tcgen05 tensor cores (bfloat16 in,
     float accumulation, bfloat16 or float out).  ``cluster``: split-K slices of a tile form a
     thread-block cluster and add their sums through distributed shared memory (up to 8 slices),
@@ -529,7 +530,9 @@ def gemm_tcgen05(a, w, out, workspace=None, status=None, splits=None, cluster=Tr
     lib = kernels_library()
     m, k = a.shape
     n = w.shape[0]
-    # swiglu: w's rows come in blocks of 64 gate rows and their 64 up rows; out is silu(gate) * up, [m, n / 2]
+    # swiglu: w's rows come in blocks of 64 gate rows and their 64 up rows; out is act(gate) * up, [m, n / 2]
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"gemm_tcgen05: unknown activation {activation!r}")
     want_shape = (m, n // 2) if swiglu else (m, n)
     if w.shape[1] != k or out.shape != want_shape or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError(f"gemm_tcgen05: {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} of {a.dtype}")
@@ -551,7 +554,8 @@ def gemm_tcgen05(a, w, out, workspace=None, status=None, splits=None, cluster=Tr
         _ptr(a, name="a"), _ptr(w, name="w"), _ptr(out, name="out"), c_int(m), c_int(n), c_int(k), c_int(a.stride(0)),
         c_int(w.stride(0)), c_int(out.stride(0)), c_int(1 if out.dtype == torch.float32 else 0), c_int(splits),
         _ptr(partial), _ptr(counters), _ptr(status, torch.int32, "status"),
-        c_int((1 if cluster else 0) | (2 if dependent else 0) | (4 if swiglu else 0)), _stream()))
+        c_int((1 if cluster else 0) | (2 if dependent else 0) | (4 if swiglu else 0) | (8 if ACTIVATIONS[activation] == 1 else 0)),
+        _stream()))
     _launched()
     return status
 
@@ -822,14 +826,15 @@ class Kernels:
         else:
             torch.bmm(a.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
 
-    def gemm_tcgen05(self, a, w, out, workspace=None, status=None, splits=None, cluster=True, dependent=False, swiglu=False):
+    def gemm_tcgen05(self, a, w, out, workspace=None, status=None, splits=None, cluster=True, dependent=False, swiglu=False,
+                     activation="silu"):
         """The tcgen05 product with the number of K slices that this engine's tuning found best for the shape."""
         if splits is None:
             key = (w.shape[0], a.shape[1], _mpad(a.shape[0])) + (("swiglu",) if swiglu else ())
             splits = self.tuned_splits.get(key)
             if splits is not None and cluster:
                 splits = min(splits, 8)
-        return gemm_tcgen05(a, w, out, workspace, status, splits, cluster, dependent, swiglu)
+        return gemm_tcgen05(a, w, out, workspace, status, splits, cluster, dependent, swiglu, activation)
 
     # ---- attention ------------------------------------------------------------------------------------------
     def decode_takes_projection(self, batch, dtype, hd: int, group: int, page_size: int, rotary_dim: int, cos_sin) -> bool:

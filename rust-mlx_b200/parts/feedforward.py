@@ -51,17 +51,16 @@ class SwiGLUFeedForward(FeedForward):
         return [self.w_gate_up, self.w_down]
 
     def gate_up_weights(self):
-        return [self.w_gate_up] if self.block and self.activation == "silu" else []
+        return [self.w_gate_up] if self.block else []
 
     def forward(self, x, batch=None, out_name: str = "ffn_out"):
         ops, ws, dt = self.ctx.ops, self.ctx.workspace, self.ctx.dtype
         n = x.shape[0]
         status = batch.status if batch is not None else None
         act = ws.get("ffn_act", (n, self.inner), dt)
-        # (the product's own epilogue knows silu only)
-        if (self.block and dt == torch.bfloat16 and self.activation == "silu"
-                and ops.prefers_fused_swiglu(n, 2 * self.inner, self.width)):
-            ops.gemm_tcgen05(x, self.w_gate_up, act, ws, status, dependent=ops.dependent_launch, swiglu=True)
+        if self.block and dt == torch.bfloat16 and ops.prefers_fused_swiglu(n, 2 * self.inner, self.width):
+            ops.gemm_tcgen05(x, self.w_gate_up, act, ws, status, dependent=ops.dependent_launch, swiglu=True,
+                             activation=self.activation)
         else:
             gu = ws.get("gate_up", (n, 2 * self.inner), dt)
             ops.linear(x, self.w_gate_up, gu, ws, status)

@@ -302,6 +302,22 @@ def test_gated_feed_forward_part_with_gelu_and_other_names():
         assert tiny.max_abs(ff.forward(x).cpu(), want) < 1e-5
 
 
+def test_gated_feed_forward_in_bfloat16_forms_gelu_in_the_product():
+    """Few rows: gate/up with GELU(gate) * up in the tcgen05 product's epilogue, one launch, against the plain pieces."""
+    from rust_mlx_b200.kernels import ops
+    from rust_mlx_b200.parts.feedforward import SwiGLUFeedForward
+    ff = SwiGLUFeedForward("m", 256, 640, activation="gelu_tanh", names=("gate", "up", "down"))
+    w = bind(ff, seed=6, dtype=torch.bfloat16, scale={".gate": 30.0})
+    assert ops.prefers_fused_swiglu(9, 1280, 256)
+    for rows in (1, 9, 40):
+        x = torch.randn(rows, 256, device=DEV).to(torch.bfloat16)
+        before = ops.launch_count
+        y = ff.forward(x)
+        assert ops.launch_count - before <= 2
+        want = plain.gated_unit(x.double().cpu(), w["m.gate"], w["m.up"], w["m.down"], plain.gelu_tanh, bf16=True)
+        assert ((y.double().cpu() - want).abs() <= 2e-2 * (1 + want.abs())).all()
+
+
 @pytest.mark.parametrize("experts, top, shared, rows", [(6, 2, 32, 50), (4, 4, 0, 9), (5, 1, 16, 1), (3, 2, 8, 700)])
 def test_routed_feed_forward_part(experts, top, shared, rows):
     from rust_mlx_b200.parts.feedforward import SwiGLUFeedForward
