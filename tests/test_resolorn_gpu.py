@@ -440,10 +440,10 @@ def requests_for(raw, lengths, seed):
 
 WAYS = {"whole": replay.whole, "tail": lambda r: replay.tail_one_by_one(r, 40), "portions": replay.portions, "mixed": replay.mixed}
 # lengths past every window and several pages; one and two tokens (the first tokens of a sequence)
-LENGTHS = {"R1": [150, 1, 2, 61, 34, 97], "R2": [300, 2, 131, 75, 1], "R3": [260, 70, 1, 129], "R4": [90, 33, 2]}
+LENGTHS = {"R1": [150, 1, 2, 61, 34, 97], "R2": [300, 2, 131, 75, 1], "R3": [260, 70, 1, 129], "R4": [90, 33, 2], "R5": [120, 3, 66]}
 
 
-@pytest.mark.parametrize("name", ["R1", "R2", "R3", "R4"])
+@pytest.mark.parametrize("name", ["R1", "R2", "R3", "R4", "R5"])
 def test_float32_replay_every_way_against_the_plain_implementation(folders, name):
     from rust_mlx_b200.engine import Engine
     raw, page = tr.CONFIGS[name]
@@ -467,7 +467,7 @@ def test_float32_replay_every_way_against_the_plain_implementation(folders, name
                 assert torch.equal(got[rid], first[rid]), (name, way, rid)
 
 
-@pytest.mark.parametrize("name", ["R1", "R2", "R3", "R4"])
+@pytest.mark.parametrize("name", ["R1", "R2", "R3", "R4", "R5"])
 def test_bfloat16_replay_every_way(folders, name):
     """Against the plain implementation with bfloat16 roundings.  A router's close call may fall the other way in
     two bfloat16 evaluations, which changes a row by far more than rounding: models with routed experts are

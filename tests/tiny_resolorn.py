@@ -60,7 +60,16 @@ R4 = {"architecture": "Resolorn", "vocab": 150, "width": 80, "max_positions": 25
                  _layer(_mixer(40, 4, 4, 16, 24), {"kind": "dense", "ff": 56})]}
 PAGE_R4 = 16
 
-CONFIGS = {"R1": (R1, PAGE_R1), "R2": (R2, PAGE_R2), "R3": (R3, PAGE_R3), "R4": (R4, PAGE_R4)}
+# R5: sizes that are multiples of nothing much (width 90, vocabulary 97, heads of 6 and 10 numbers, latents of 40 and 18):
+# the kernels' plain arrangements in both dtypes, a window shorter than a page, a factor above 1, a larger eps
+R5 = {"architecture": "Resolorn", "vocab": 97, "width": 90, "max_positions": 200, "norm": {"eps": 1e-4},
+      "residual_mult": 1.3,
+      "layers": [_layer(_mixer(3, 6, 10, 30, 40, window=7, scale=0.5), _moe(20, 3, 2, shared=14)),
+                 _layer(_mixer(5, 10, 6, 22, 18), {"kind": "dense", "ff": 36}),
+                 _layer(_mixer(2, 14, 14, 10, 40, window=50, kv_from=0), None)]}
+PAGE_R5 = 16
+
+CONFIGS = {"R1": (R1, PAGE_R1), "R2": (R2, PAGE_R2), "R3": (R3, PAGE_R3), "R4": (R4, PAGE_R4), "R5": (R5, PAGE_R5)}
 
 
 def make_folder(tmp_path, raw: dict, seed: int = 0, sharp: float = 8.0, out_boost: float = 20.0) -> str:
