@@ -4,7 +4,7 @@ Caches (one per schedule cache id) with equal needs form a group: a paged group
 has one pool of keys and one of values, [caches, pages, kv_heads, page_size,
 head_dim] — inside a page each kv head's slots are contiguous, so one head's
 keys of a page are one block of memory — and one block table per request; a
-state group has [caches, slots, *state_shape].  A mixer sees its cache through
+state group has [caches, slots + 1, *state_shape] (the last slot belongs to no request).  A mixer sees its cache through
 a view: its own slice of the pools and the batch's tables or slots.
 """
 from __future__ import annotations
@@ -84,8 +84,9 @@ class CachePools:
                 grp.k_pool = torch.zeros(shape, dtype=dtype, device=device)
                 grp.v_pool = torch.zeros(shape, dtype=dtype, device=device) if grp.spec.values else None
             elif grp.spec.kind == "state":
-                sd = _STATE_DTYPES[grp.spec.state_dtype]
-                grp.state = torch.zeros((n, self.max_requests, *grp.spec.state_shape), dtype=sd, device=device)
+                sd = dtype if grp.spec.state_dtype == "compute" else _STATE_DTYPES[grp.spec.state_dtype]
+                # (one slot more than there are requests: the spare places of a padded decode graph step there)
+                grp.state = torch.zeros((n, self.max_requests + 1, *grp.spec.state_shape), dtype=sd, device=device)
             else:
                 raise ValueError(f"unknown cache kind {grp.spec.kind!r}")
         self.paged_groups = [g for g in self.groups if g.spec.kind == "paged"]
@@ -117,7 +118,8 @@ class CachePools:
             return PagedView(grp.k_pool[i], grp.v_pool[i] if grp.v_pool is not None else None,
                              batch.block_tables[grp.table_index], self.page_size,
                              grp.spec.window, read_only)
-        return StateView(grp.state[i], batch.slots, batch.slots_host, read_only)
+        slots = getattr(batch, "state_slots", None)
+        return StateView(grp.state[i], batch.slots if slots is None else slots, batch.slots_host, read_only)
 
     def bytes_per_token(self) -> int:
         total = 0

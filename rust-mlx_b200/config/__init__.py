@@ -1,5 +1,6 @@
 from .base import ConfigError, ModelConfig, read_config_json
 from .qwen3 import Qwen3Config
 from .resolorn import ResolornConfig
+from .gugalorn import GugalornConfig
 
-__all__ = ["ConfigError", "ModelConfig", "Qwen3Config", "ResolornConfig", "read_config_json"]
+__all__ = ["ConfigError", "ModelConfig", "Qwen3Config", "ResolornConfig", "GugalornConfig", "read_config_json"]

@@ -8,6 +8,8 @@
 // depends on p (and the window) only: not on how the prompt was cut into steps, on the
 // other tokens of the batch, on the page size or on which pages hold the keys.
 //
+// `sinks` (or null): a score per query head that enters the softmax's denominator and has no value.
+//
 // Grid: (tokens, kv heads); a block has one warp per query head of the group, so the
 // group's warps read the same keys from shared memory.
 #include "common.cuh"
@@ -20,7 +22,8 @@ __global__ void attention_plain_kernel(const T* __restrict__ q, const T* __restr
                                        const T* __restrict__ v_pool, const int* __restrict__ positions,
                                        const int* __restrict__ seq_index, const int* __restrict__ block_table,
                                        int table_stride, int page_size, T* __restrict__ out, int nq, int nkv,
-                                       int hd, int window, float scale, int* __restrict__ status) {
+                                       int hd, int window, float scale, int* __restrict__ status,
+                                       const float* __restrict__ sinks) {
     extern __shared__ float smem[];
     const int group = nq / nkv;
     const int t = blockIdx.x, kvh = blockIdx.y;
@@ -86,6 +89,14 @@ __global__ void attention_plain_kernel(const T* __restrict__ q, const T* __restr
             }
         }
     }
+    if (sinks) {
+        // a sink: one more term in the denominator, exp(sinks[head]), that has no value (its score is not scaled)
+        const float m_new = fmaxf(m, sinks[head]);
+        const float corr = expf(m - m_new);
+        l = l * corr + expf(sinks[head] - m_new);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[i] *= corr;
+    }
     const float inv_l = 1.f / l;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
@@ -98,7 +109,7 @@ __global__ void attention_plain_kernel(const T* __restrict__ q, const T* __restr
 RMX_API int rmx_attention_plain(const void* q, const void* k_pool, const void* v_pool, const int* positions,
                                 const int* seq_index, const int* block_table, int table_stride, int page_size,
                                 void* out, int n_tokens, int nq, int nkv, int hd, int window, float scale,
-                                int* status, int dtype, void* stream) {
+                                int* status, const float* sinks, int dtype, void* stream) {
     if (n_tokens == 0) return 0;
     RMX_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_plain: %d query heads over %d kv heads", nq, nkv);
     const int group = nq / nkv;
@@ -115,13 +126,13 @@ RMX_API int rmx_attention_plain(const void* q, const void* k_pool, const void* v
             cudaFuncSetAttribute(attention_plain_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attention_plain_kernel<float><<<grid, group * 32, smem, s>>>(
             (const float*)q, (const float*)k_pool, (const float*)v_pool, positions, seq_index, block_table, table_stride,
-            page_size, (float*)out, nq, nkv, hd, window, scale, status);
+            page_size, (float*)out, nq, nkv, hd, window, scale, status, sinks);
     } else if (dtype == RMX_BF16) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(attention_plain_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attention_plain_kernel<__nv_bfloat16><<<grid, group * 32, smem, s>>>(
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, positions, seq_index,
-            block_table, table_stride, page_size, (__nv_bfloat16*)out, nq, nkv, hd, window, scale, status);
+            block_table, table_stride, page_size, (__nv_bfloat16*)out, nq, nkv, hd, window, scale, status, sinks);
     } else {
         RMX_FAIL("attention_plain: unknown dtype %d", dtype);
     }

@@ -38,7 +38,7 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
                                  float* __restrict__ h, int width, int vocab, const int* __restrict__ from_last,
                                  const int* __restrict__ seq_index, const int* __restrict__ slots,
                                  const int* __restrict__ last_tokens, const T* __restrict__ pos_table,
-                                 const int* __restrict__ positions, int max_positions) {
+                                 const int* __restrict__ positions, int max_positions, float scale) {
     allow_dependents();        // (what follows waits for this kernel before it touches memory)
     wait_for_prior_kernels();
     const int t = blockIdx.x;
@@ -54,6 +54,7 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
         for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (ok) load4(row + i, v);
+            v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;   // (1 unless the model scales its embeddings: exact then)
             if (prow) {
                 float4 a;
                 load4(prow + i, a);
@@ -63,13 +64,13 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
         }
     } else {
         for (int i = threadIdx.x; i < width; i += blockDim.x)
-            out[i] = (ok ? to_float(row[i]) : 0.f) + (prow ? to_float(prow[i]) : 0.f);
+            out[i] = (ok ? to_float(row[i]) : 0.f) * scale + (prow ? to_float(prow[i]) : 0.f);
     }
 }
 
 RMX_API int rmx_embedding(const int* ids, const void* table, float* h, int n_tokens, int width, int vocab,
                           const int* from_last, const int* seq_index, const int* slots, const int* last_tokens,
-                          const void* pos_table, const int* positions, int max_positions, int dtype, void* stream) {
+                          const void* pos_table, const int* positions, int max_positions, float scale, int dtype, void* stream) {
     if (n_tokens == 0) return 0;
     RMX_REQUIRE(n_tokens > 0 && width > 0 && vocab > 0, "embedding: bad sizes");
     RMX_REQUIRE(pos_table == nullptr || (positions && max_positions > 0), "embedding: a position table needs positions and its row count");
@@ -79,11 +80,11 @@ RMX_API int rmx_embedding(const int* ids, const void* table, float* h, int n_tok
     if (dtype == RMX_F32)
         RMX_CHECK_LAUNCHED(launch_dependent(embedding_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, ids, (const float*)table, h, width,
                                             vocab, from_last, seq_index, slots, last_tokens, (const float*)pos_table, positions,
-                                            max_positions), "embedding");
+                                            max_positions, scale), "embedding");
     else if (dtype == RMX_BF16)
         RMX_CHECK_LAUNCHED(launch_dependent(embedding_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, ids,
                                             (const __nv_bfloat16*)table, h, width, vocab, from_last, seq_index, slots, last_tokens,
-                                            (const __nv_bfloat16*)pos_table, positions, max_positions), "embedding");
+                                            (const __nv_bfloat16*)pos_table, positions, max_positions, scale), "embedding");
     else
         RMX_FAIL("embedding: unknown dtype %d", dtype);
     RMX_CHECK_LAUNCH("embedding");
@@ -91,12 +92,12 @@ RMX_API int rmx_embedding(const int* ids, const void* table, float* h, int n_tok
 }
 
 // One block per output row.  src_row = rows ? rows[r] : r.
-//   v = h[src_row] + mult * (delta[src_row] + delta2[src_row])   (float; either delta may be null; mult 1 changes nothing)
+//   v = h[src_row] + mult * (delta[src_row] + mult2 * delta2[src_row])   (float; either delta may be null; factors of 1 change nothing)
 //   if (write_h) h[src_row] = v
 //   x[r] = v * rsqrt(mean(v^2) + eps) * w     (rounded once to T)
 // The reduction order depends on the width and the block size only.
 template <typename T>
-__global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ delta, const T* __restrict__ delta2, float mult,
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ delta, const T* __restrict__ delta2, float mult, float mult2,
                                    const int* __restrict__ rows, const float* __restrict__ w, float eps,
                                    T* __restrict__ x, int width, int write_h) {
     __shared__ float scratch[32];
@@ -121,7 +122,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
                 if (drow2) {
                     float4 e;
                     load4(drow2 + i, e);
-                    d.x += e.x; d.y += e.y; d.z += e.z; d.w += e.w;
+                    d.x += mult2 * e.x; d.y += mult2 * e.y; d.z += mult2 * e.z; d.w += mult2 * e.w;
                 }
                 v.x += mult * d.x; v.y += mult * d.y; v.z += mult * d.z; v.w += mult * d.w;
             }
@@ -141,7 +142,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
     } else {
         for (int i = threadIdx.x; i < width; i += blockDim.x) {
             float v = hrow[i];
-            if (drow) v += mult * (to_float(drow[i]) + (drow2 ? to_float(drow2[i]) : 0.f));
+            if (drow) v += mult * (to_float(drow[i]) + (drow2 ? mult2 * to_float(drow2[i]) : 0.f));
             vals[i] = v;
             if (write_h) hrow[i] = v;
             ss += v * v;
@@ -155,7 +156,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const T* __restrict__ 
 // of four in registers, all their loads under way at once, and the blocks are small enough for several to share an
 // SM.  The reduction order depends on the width and the block size only, as above.
 template <typename T, int CHUNKS>
-__global__ void add_rmsnorm_rows_kernel(float* __restrict__ h, const T* __restrict__ delta, const T* __restrict__ delta2, float mult,
+__global__ void add_rmsnorm_rows_kernel(float* __restrict__ h, const T* __restrict__ delta, const T* __restrict__ delta2, float mult, float mult2,
                                         const int* __restrict__ rows, const float* __restrict__ w, float eps,
                                         T* __restrict__ x, int width, int write_h) {
     __shared__ float scratch[32];
@@ -187,7 +188,7 @@ __global__ void add_rmsnorm_rows_kernel(float* __restrict__ h, const T* __restri
             if (drow2) {
                 float4 e;
                 load4(drow2 + i, e);
-                d[c].x += e.x; d[c].y += e.y; d[c].z += e.z; d[c].w += e.w;
+                d[c].x += mult2 * e.x; d[c].y += mult2 * e.y; d[c].z += mult2 * e.z; d[c].w += mult2 * e.w;
             }
         }
     }
@@ -213,7 +214,7 @@ __global__ void add_rmsnorm_rows_kernel(float* __restrict__ h, const T* __restri
 }
 
 template <typename T>
-int launch_add_rmsnorm(float* h, const T* delta, const T* delta2, float mult, const int* rows, const float* w, float eps, T* x,
+int launch_add_rmsnorm(float* h, const T* delta, const T* delta2, float mult, float mult2, const int* rows, const float* w, float eps, T* x,
                        int n_rows, int width, int write_h, cudaStream_t s) {
     const int groups = width / 4;
     // Which arrangement runs decides the order in which a row's squares are added.  In the 32-bit path that order
@@ -223,7 +224,7 @@ int launch_add_rmsnorm(float* h, const T* delta, const T* delta2, float mult, co
     if ((width & 3) == 0 && groups <= 1024 && (n_rows <= 256 || !by_rows)) {
         // few rows (decoding): as many threads as the row has groups of four, so that a row's latency is one load
         const int threads = (groups + 31) / 32 * 32;
-        RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_rows_kernel<T, 1>, dim3(n_rows), dim3(threads), 0, s, h, delta, delta2, mult, rows, w, eps,
+        RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_rows_kernel<T, 1>, dim3(n_rows), dim3(threads), 0, s, h, delta, delta2, mult, mult2, rows, w, eps,
                                             x, width, write_h), "add_rmsnorm");
         return 0;
     }
@@ -232,21 +233,21 @@ int launch_add_rmsnorm(float* h, const T* delta, const T* delta2, float mult, co
         // many rows: as few threads as hold the row in CHUNKS groups each (at least a warp), several blocks an SM
         int threads = ((groups + CHUNKS - 1) / CHUNKS + 31) / 32 * 32;
         threads = threads < 32 ? 32 : threads;
-        RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_rows_kernel<T, CHUNKS>, dim3(n_rows), dim3(threads), 0, s, h, delta, delta2, mult, rows, w, eps,
+        RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_rows_kernel<T, CHUNKS>, dim3(n_rows), dim3(threads), 0, s, h, delta, delta2, mult, mult2, rows, w, eps,
                                             x, width, write_h), "add_rmsnorm");
         return 0;
     }
     const int threads = block_threads(width);
     const size_t smem = (size_t)width * sizeof(float);
     if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_kernel<T>, dim3(n_rows), dim3(threads), smem, s, h, delta, delta2, mult, rows, w, eps, x, width,
+    RMX_CHECK_LAUNCHED(launch_dependent(add_rmsnorm_kernel<T>, dim3(n_rows), dim3(threads), smem, s, h, delta, delta2, mult, mult2, rows, w, eps, x, width,
                                         write_h), "add_rmsnorm");
     return 0;
 }
 
-// delta2 (or null) and mult: what is added to the stream is mult * (delta + delta2), formed in float (a layer whose
+// delta2 (or null), mult and mult2: what is added to the stream is mult * (delta + mult2 * delta2), formed in float (a layer whose
 // mixer and feed-forward read the same norm adds both at once, scaled by the model's factor).
-RMX_API int rmx_add_rmsnorm(float* h, const void* delta, const void* delta2, float mult, const int* rows, const float* w, float eps,
+RMX_API int rmx_add_rmsnorm(float* h, const void* delta, const void* delta2, float mult, float mult2, const int* rows, const float* w, float eps,
                             void* x, int n_rows, int width, int write_h, int dtype, void* stream) {
     if (n_rows == 0) return 0;
     RMX_REQUIRE(delta != nullptr || delta2 == nullptr, "add_rmsnorm: a second delta without a first");
@@ -255,9 +256,9 @@ RMX_API int rmx_add_rmsnorm(float* h, const void* delta, const void* delta2, flo
     RMX_REQUIRE(!(rows && write_h), "add_rmsnorm: rows and write_h do not go together");
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
-    if (dtype == RMX_F32) rc = launch_add_rmsnorm<float>(h, (const float*)delta, (const float*)delta2, mult, rows, w, eps, (float*)x, n_rows, width, write_h, s);
+    if (dtype == RMX_F32) rc = launch_add_rmsnorm<float>(h, (const float*)delta, (const float*)delta2, mult, mult2, rows, w, eps, (float*)x, n_rows, width, write_h, s);
     else if (dtype == RMX_BF16)
-        rc = launch_add_rmsnorm<__nv_bfloat16>(h, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)delta2, mult, rows, w, eps,
+        rc = launch_add_rmsnorm<__nv_bfloat16>(h, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)delta2, mult, mult2, rows, w, eps,
                                                (__nv_bfloat16*)x, n_rows, width, write_h, s);
     else RMX_FAIL("add_rmsnorm: unknown dtype %d", dtype);
     if (rc != 0) return rc;

@@ -277,7 +277,117 @@ __global__ void __launch_bounds__(WARPS * 32, 8) qk_rope_cache_128_wide_kernel(
         }
     }
 }
+// The norm taken over the whole projection instead of a head at a time: q (all nq * dq numbers of a token at once) and k
+// (all nkv * dq) are each divided by their root mean square and multiplied by a weight of the projection's size, then
+// split into heads and rotated as above.  Query/key heads have dq numbers, value heads dv; the cache's heads have
+// hd >= max(dq, dv) numbers, the rest of a head is written as zeros (a zero in q and k adds nothing to a score, and the
+// zero columns of a value head come out as zeros).  Input rows are [q | k | v].  One block a token.
+template <typename T>
+__global__ void __launch_bounds__(256) qk_whole_norm_rope_cache_kernel(
+    const T* __restrict__ qkv, int row_stride, const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
+    const float* __restrict__ inv_freq, int rotary_dim, const float* __restrict__ cos_sin, const int* __restrict__ positions,
+    const int* __restrict__ seq_index, const int* __restrict__ block_table, int table_stride, int page_size,
+    T* __restrict__ k_pool, T* __restrict__ v_pool, T* __restrict__ q_out, int nq, int nkv, int dq, int dv, int hd,
+    int write_kv, int* __restrict__ status) {
+    extern __shared__ float smem[];
+    __shared__ float scratch[32];
+    allow_dependents();
+    wait_for_prior_kernels();
+    const int t = blockIdx.x;
+    const int nqd = nq * dq, nkd = nkv * dq;
+    const T* row = qkv + (size_t)t * row_stride;
+    float* qb = smem;            // [nq * dq]
+    float* kb = smem + nqd;      // [nkv * dq]
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < nqd; i += blockDim.x) {
+        const float v = to_float(row[i]);
+        qb[i] = v;
+        sq += v * v;
+    }
+    for (int i = threadIdx.x; i < nkd; i += blockDim.x) {
+        const float v = to_float(row[nqd + i]);
+        kb[i] = v;
+        sk += v * v;
+    }
+    const float inv_q = q_norm ? rsqrtf(block_sum(sq, scratch) / (float)nqd + eps) : 1.f;
+    const float inv_k = k_norm ? rsqrtf(block_sum(sk, scratch) / (float)nkd + eps) : 1.f;
+    __syncthreads();
+    for (int i = threadIdx.x; i < nqd; i += blockDim.x) qb[i] = q_norm ? qb[i] * inv_q * q_norm[i] : qb[i];
+    for (int i = threadIdx.x; i < nkd; i += blockDim.x) kb[i] = k_norm ? kb[i] * inv_k * k_norm[i] : kb[i];
+    __syncthreads();
+    const int pos = positions[t];
+    const int half = rotary_dim >> 1;
+    size_t page_off = 0;
+    if (write_kv) {
+        const int page = block_table[(size_t)seq_index[t] * table_stride + pos / page_size];
+        if (page < 0) {
+            if (threadIdx.x == 0) atomicExch(status, 1);
+            write_kv = 0;
+        }
+        page_off = (size_t)(page < 0 ? 0 : page) * nkv;
+    }
+    const int heads = nq + (write_kv ? nkv : 0);
+    for (int e = threadIdx.x; e < heads * hd; e += blockDim.x) {
+        const int head = e / hd, d = e - head * hd;
+        const float* src = head < nq ? qb + head * dq : kb + (head - nq) * dq;
+        float v = 0.f;
+        if (d < dq) {
+            v = src[d];
+            if (d < rotary_dim) {
+                const int j = d < half ? d : d - half;
+                float sn, cs;
+                if (cos_sin) {
+                    cs = cos_sin[(size_t)t * rotary_dim + j];
+                    sn = cos_sin[(size_t)t * rotary_dim + half + j];
+                } else {
+                    sincosf((float)pos * inv_freq[j], &sn, &cs);
+                }
+                v = d < half ? src[d] * cs - src[d + half] * sn : src[d] * cs + src[d - half] * sn;
+            }
+        }
+        if (head < nq) q_out[((size_t)t * nq + head) * hd + d] = from_float<T>(v);
+        else k_pool[((page_off + (head - nq)) * page_size + pos % page_size) * hd + d] = from_float<T>(v);
+    }
+    if (write_kv) {
+        const T* vrow = row + nqd + nkd;
+        for (int e = threadIdx.x; e < nkv * hd; e += blockDim.x) {
+            const int head = e / hd, d = e - head * hd;
+            v_pool[((page_off + head) * page_size + pos % page_size) * hd + d] = d < dv ? vrow[head * dv + d] : from_float<T>(0.f);
+        }
+    }
+}
 }  // namespace
+
+RMX_API int rmx_qk_whole_norm_rope_cache(const void* qkv, int row_stride, const float* q_norm, const float* k_norm, float eps,
+                                         const float* inv_freq, int rotary_dim, const float* cos_sin, const int* positions,
+                                         const int* seq_index, const int* block_table, int table_stride, int page_size, void* k_pool,
+                                         void* v_pool, void* q_out, int n_tokens, int nq, int nkv, int dq, int dv, int hd, int write_kv,
+                                         int* status, int dtype, void* stream) {
+    if (n_tokens == 0) return 0;
+    RMX_REQUIRE(nq > 0 && nkv > 0 && dq > 0 && dv > 0 && hd >= dq && hd >= dv, "qk_whole_norm_rope_cache: bad head sizes");
+    RMX_REQUIRE(rotary_dim >= 0 && rotary_dim <= dq && rotary_dim % 2 == 0, "qk_whole_norm_rope_cache: rotary_dim %d must be even and at most %d", rotary_dim, dq);
+    RMX_REQUIRE(rotary_dim == 0 || inv_freq != nullptr || cos_sin != nullptr, "qk_whole_norm_rope_cache: rotation without a table");
+    RMX_REQUIRE(page_size > 0 && table_stride > 0, "qk_whole_norm_rope_cache: bad page geometry");
+    RMX_REQUIRE(row_stride >= (nq + nkv) * dq + nkv * dv, "qk_whole_norm_rope_cache: row stride %d too small", row_stride);
+    const size_t smem = (size_t)(nq + nkv) * dq * sizeof(float);
+    RMX_REQUIRE(smem <= 200 * 1024, "qk_whole_norm_rope_cache: a projection of %d numbers is beyond 51200", (nq + nkv) * dq);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RMX_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(qk_whole_norm_rope_cache_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        RMX_CHECK_LAUNCHED(launch_dependent(qk_whole_norm_rope_cache_kernel<float>, dim3(n_tokens), dim3(256), smem, s, (const float*)qkv, row_stride,
+            q_norm, k_norm, eps, inv_freq, rotary_dim, cos_sin, positions, seq_index, block_table, table_stride, page_size, (float*)k_pool,
+            (float*)v_pool, (float*)q_out, nq, nkv, dq, dv, hd, write_kv, status), "qk_whole_norm_rope_cache");
+    } else if (dtype == RMX_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(qk_whole_norm_rope_cache_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        RMX_CHECK_LAUNCHED(launch_dependent(qk_whole_norm_rope_cache_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), smem, s,
+            (const __nv_bfloat16*)qkv, row_stride, q_norm, k_norm, eps, inv_freq, rotary_dim, cos_sin, positions, seq_index, block_table,
+            table_stride, page_size, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, (__nv_bfloat16*)q_out, nq, nkv, dq, dv, hd, write_kv,
+            status), "qk_whole_norm_rope_cache");
+    } else {
+        RMX_FAIL("qk_whole_norm_rope_cache: unknown dtype %d", dtype);
+    }
+    return 0;
+}
 
 RMX_API int rmx_rope_table(const int* positions, const float* inv_freq, float* cos_sin, int n_tokens, int rotary_dim,
                            void* stream) {

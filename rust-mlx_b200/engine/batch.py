@@ -59,6 +59,8 @@ class StepBatch:
     per_step: dict = field(default_factory=dict)
     # int32 [state slots] on the device: the token the last sampling chose for the request in each slot (the engine's)
     last_tokens: torch.Tensor = None
+    # int32 [sequences] on the device: where every sequence's state of fixed size lives; None: ``slots``
+    state_slots: torch.Tensor = None
 
     @property
     def all_decode(self) -> bool:

@@ -108,12 +108,21 @@ class DecodeGraphs:
         cap.dev.copy_(cap.hosts[0], non_blocking=True)
         cap.events[0].record()
         cap.batch = cap.layout.views(cap.dev, e._status, facts)
+        # a spare place repeats the first sequence (the same token to the same position: the same keys are written twice),
+        # but a state of fixed size must not be stepped twice: spare places step the slot that belongs to no request,
+        # which is what ``row_slots`` names for them (a decode step has one wanted row a sequence)
+        cap.batch.state_slots = cap.batch.row_slots
         # once eagerly: buffers reach their size, kernels' attributes are set, libraries warm up.
         # It writes this step's keys and values, which the replay below writes again, the same; the tokens it
         # chooses are put back, because a step that runs ahead takes its ids from there.
+        # A state of fixed size is not written the same twice (it is stepped): the sequences' slots are put back too.
         saved = e.last_tokens.clone()
+        slots = torch.tensor(sorted(set(facts["slots_host"])), dtype=torch.long, device=e.device)
+        states = [grp.state.index_select(1, slots) for grp in e.pools.state_groups]
         self._step(cap)
         e.last_tokens.copy_(saved)
+        for grp, kept in zip(e.pools.state_groups, states):
+            grp.state.index_copy_(1, slots, kept)
         torch.cuda.synchronize()
         cap.generation = e.workspace.generation
         e.workspace.frozen = True

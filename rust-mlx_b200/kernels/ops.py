@@ -55,10 +55,11 @@ def count_launches(n: int) -> None:
 
 
 def embedding(ids, table, h_out, from_last=None, seq_index=None, slots=None, last_tokens=None, pos_table=None,
-              positions=None):
+              positions=None, scale=1.0):
     """h_out[t] = table[ids[t]] as float32 (the residual stream).  Where from_last[t] is set the id is the one the
     last step's sampling left for the token's sequence: last_tokens[slots[seq_index[t]]].  With ``pos_table`` the
-    learned vector of the token's position, pos_table[positions[t]], is added (in float)."""
+    learned vector of the token's position, pos_table[positions[t]], is added (in float).  ``scale`` multiplies the
+    token's row (in float) before anything is added."""
     lib = kernels_library()
     n, width = h_out.shape
     if pos_table is not None and (pos_table.dtype != table.dtype or pos_table.shape[1] != width):
@@ -68,12 +69,12 @@ def embedding(ids, table, h_out, from_last=None, seq_index=None, slots=None, las
                             _ptr(seq_index, torch.int32, "seq_index"), _ptr(slots, torch.int32, "slots"),
                             _ptr(last_tokens, torch.int32, "last_tokens"), _ptr(pos_table, name="pos_table"),
                             _ptr(positions if pos_table is not None else None, torch.int32, "positions"),
-                            c_int(pos_table.shape[0] if pos_table is not None else 0), c_int(dtype_code(table)), _stream()))
+                            c_int(pos_table.shape[0] if pos_table is not None else 0), c_float(scale), c_int(dtype_code(table)), _stream()))
     _launched()
 
 
-def add_rmsnorm(h, delta, weight, eps, x_out, rows=None, write_h=True, delta2=None, mult=1.0):
-    """v = h + mult * (delta + delta2); h = v (if write_h); x_out = RMSNorm(v; weight, eps).  With ``rows`` the
+def add_rmsnorm(h, delta, weight, eps, x_out, rows=None, write_h=True, delta2=None, mult=1.0, mult2=1.0):
+    """v = h + mult * (delta + mult2 * delta2); h = v (if write_h); x_out = RMSNorm(v; weight, eps).  With ``rows`` the
     rows rows[r] are read, x_out[r] is written and h is left alone."""
     lib = kernels_library()
     n = x_out.shape[0]
@@ -82,7 +83,7 @@ def add_rmsnorm(h, delta, weight, eps, x_out, rows=None, write_h=True, delta2=No
         raise KernelError("add_rmsnorm: delta and output must have the same dtype")
     if delta2 is not None and (delta is None or delta2.dtype != delta.dtype or delta2.shape != delta.shape):
         raise KernelError("add_rmsnorm: a second delta goes with a first of the same shape and dtype")
-    check(lib.rmx_add_rmsnorm(_ptr(h, torch.float32, "h"), _ptr(delta, name="delta"), _ptr(delta2, name="delta2"), c_float(mult),
+    check(lib.rmx_add_rmsnorm(_ptr(h, torch.float32, "h"), _ptr(delta, name="delta"), _ptr(delta2, name="delta2"), c_float(mult), c_float(mult2),
                               _ptr(rows, torch.int32, "rows"),
                               _ptr(weight, torch.float32, "weight"), c_float(eps), _ptr(x_out, name="x"),
                               c_int(n), c_int(width), c_int(1 if (write_h and rows is None) else 0),
@@ -312,7 +313,8 @@ def qk_rope_cache(qkv, q_norm, k_norm, eps, inv_freq, rotary_dim, positions, seq
 
 
 def attention_plain(q, k_pool, v_pool, positions, seq_index, block_table, page_size, out, nq, nkv, hd, window,
-                    scale, status):
+                    scale, status, sinks=None):
+    """``sinks`` (float32 [nq], or None): a score a query head that enters the softmax's denominator and has no value."""
     lib = kernels_library()
     n = q.shape[0]
     check(lib.rmx_attention_plain(
@@ -320,7 +322,133 @@ def attention_plain(q, k_pool, v_pool, positions, seq_index, block_table, page_s
         _ptr(positions, torch.int32, "positions"), _ptr(seq_index, torch.int32, "seq_index"),
         _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), c_int(page_size),
         _ptr(out, q.dtype, "out"), c_int(n), c_int(nq), c_int(nkv), c_int(hd), c_int(window), c_float(scale),
-        _ptr(status, torch.int32, "status"), c_int(dtype_code(q)), _stream()))
+        _ptr(status, torch.int32, "status"), _ptr(sinks, torch.float32, "sinks"), c_int(dtype_code(q)), _stream()))
+    _launched()
+
+
+def qk_whole_norm_rope_cache(qkv, q_norm, k_norm, eps, inv_freq, rotary_dim, positions, seq_index, block_table, page_size,
+                             k_pool, v_pool, q_out, nq, nkv, dq, dv, hd, write_kv, status, cos_sin=None):
+    """Rows of ``qkv`` are [q (nq * dq) | k (nkv * dq) | v (nkv * dv)].  q and k are each RMS-normed over the WHOLE
+    projection (weights of the projection's size, or None), split into heads, rotated, and written: q to ``q_out``
+    [tokens, nq, hd], k and v into their pages, heads padded with zeros to the cache's ``hd``."""
+    lib = kernels_library()
+    n = qkv.shape[0]
+    if qkv.dim() != 2 or qkv.stride(1) != 1 or q_out.shape != (n, nq * hd):
+        raise KernelError("qk_whole_norm_rope_cache: qkv must be [tokens, columns] with unit column stride, q_out [tokens, nq * hd]")
+    check(lib.rmx_qk_whole_norm_rope_cache(
+        c_void_p(qkv.data_ptr()), c_int(qkv.stride(0)), _ptr(q_norm, torch.float32, "q_norm"), _ptr(k_norm, torch.float32, "k_norm"),
+        c_float(eps), _ptr(inv_freq, torch.float32, "inv_freq"), c_int(rotary_dim), _ptr(cos_sin, torch.float32, "cos_sin"),
+        _ptr(positions, torch.int32, "positions"), _ptr(seq_index, torch.int32, "seq_index"),
+        _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), c_int(page_size),
+        _ptr(k_pool, qkv.dtype, "k_pool"), _ptr(v_pool, qkv.dtype, "v_pool"), _ptr(q_out, qkv.dtype, "q_out"), c_int(n), c_int(nq),
+        c_int(nkv), c_int(dq), c_int(dv), c_int(hd), c_int(1 if write_kv else 0), _ptr(status, torch.int32, "status"),
+        c_int(dtype_code(qkv)), _stream()))
+    _launched()
+
+
+def sigmoid_gate(o, o_head, gate, out, heads, vdim):
+    """out[t, h, :] = o[t, h, :vdim] * sigmoid(gate[t, h, :]): ``o`` [tokens, heads * o_head] (heads padded to o_head
+    numbers), ``gate`` some columns of wider rows, ``out`` [tokens, heads * vdim] (may be ``o`` when o_head == vdim)."""
+    lib = kernels_library()
+    n = o.shape[0]
+    if o.shape != (n, heads * o_head) or out.shape != (n, heads * vdim) or gate.shape != (n, heads * vdim) or gate.stride(1) != 1 \
+            or gate.dtype != o.dtype or out.dtype != o.dtype:
+        raise KernelError("sigmoid_gate: shapes or dtypes do not fit")
+    check(lib.rmx_sigmoid_gate(_ptr(o, name="o"), c_int(o_head), c_void_p(gate.data_ptr()), c_int(gate.stride(0)), _ptr(out, name="out"),
+                               c_int(n), c_int(heads), c_int(vdim), c_int(dtype_code(o)), _stream()))
+    _launched()
+
+
+def short_conv(x, weight, bias, out, ring, batch, slots, activation=None, residual=False):
+    """A causal convolution over time on each channel: out_t = act(bias + sum_j weight[:, j] * x_(t - taps + 1 + j)) (+ x_t).
+    ``x`` and ``out``: [tokens, channels] (columns of wider rows allowed), ``weight`` float32 [channels, taps], ``ring``
+    [slots, max(taps - 1, 1), channels] of x's dtype: every sequence's last taps - 1 inputs, read for what lies before the
+    step's tokens and written with the step's last ones."""
+    lib = kernels_library()
+    n, channels = x.shape
+    taps = weight.shape[1]
+    if weight.shape != (channels, taps) or out.shape != (n, channels) or x.stride(1) != 1 or out.stride(1) != 1 or out.dtype != x.dtype \
+            or ring.dtype != x.dtype or ring.shape[1:] != (max(taps - 1, 1), channels):
+        raise KernelError("short_conv: shapes or dtypes do not fit")
+    if activation not in (None, "silu"):
+        raise KernelError(f"short_conv: unknown activation {activation!r}")
+    check(lib.rmx_short_conv(c_void_p(x.data_ptr()), c_int(x.stride(0)), _ptr(weight, torch.float32, "weight"),
+                             _ptr(bias, torch.float32, "bias"), c_void_p(out.data_ptr()), c_int(out.stride(0)), _ptr(ring, name="ring"),
+                             c_int(channels), c_int(taps), _ptr(batch.positions, torch.int32, "positions"),
+                             _ptr(batch.seq_index, torch.int32, "seq_index"), _ptr(slots, torch.int32, "slots"),
+                             _ptr(batch.q_start, torch.int32, "q_start"), c_int(n), c_int(batch.n_seqs),
+                             c_int(1 if activation == "silu" else 0), c_int(1 if residual else 0),
+                             c_int(1 if batch.max_q_len == 1 else 0), c_int(dtype_code(x)), _stream()))
+    _launched(1 if batch.max_q_len == 1 or taps == 1 else 2)
+
+
+def _recurrence_warps(batch, heads, vdim):
+    """Warps a block of the recurrence (8 columns of a head's state each): as many as cover a head's columns while the grid
+    still has a block or two an SM; fewer, so that more blocks run side by side, when few sequences step."""
+    warps = max(1, min(8, -(-vdim // 8)))
+    while warps > 1 and batch.n_seqs * heads * -(-vdim // (8 * warps)) < 2 * _sm_count():
+        warps //= 2
+    return warps
+
+
+def _cols(t, name):
+    if t.dim() != 2 or t.stride(1) != 1 or not t.is_cuda:
+        raise KernelError(f"{name} must be [tokens, columns] on a CUDA device with unit column stride")
+    return c_void_p(t.data_ptr()), c_int(t.stride(0))
+
+
+def recurrence_ssd(conv, dt, dt_bias, a_log, d_skip, state, out, batch, slots, heads, groups, k, v):
+    """Per head S_t = exp(-exp(A_log) dt_t) S_(t-1) + dt_t B_t x_t^T, y_t = S_t^T C_t + D x_t, dt = softplus(raw + bias):
+    ``conv`` rows [x (heads * v) | B (groups * k) | C (groups * k)], ``dt`` [tokens, heads] raw, ``state`` float32
+    [slots, heads, k, v] (read and written), ``out`` float32 [tokens, heads * v]."""
+    lib = kernels_library()
+    n = conv.shape[0]
+    if conv.shape[1] != heads * v + 2 * groups * k or dt.shape != (n, heads) or out.shape != (n, heads * v) or state.shape[1:] != (heads, k, v) \
+            or dt.dtype != conv.dtype:
+        raise KernelError("recurrence_ssd: shapes do not fit")
+    p0, l0 = _cols(conv, "conv")
+    p1, l1 = _cols(dt, "dt")
+    check(lib.rmx_linear_recurrence(c_int(0), _ptr(state, torch.float32, "state"), _ptr(out, torch.float32, "out"),
+                                    _ptr(batch.q_start, torch.int32, "q_start"), _ptr(slots, torch.int32, "slots"), c_int(batch.n_seqs),
+                                    c_int(heads), c_int(k), c_int(v), p0, l0, p1, l1, c_void_p(0), c_int(0),
+                                    _ptr(dt_bias, torch.float32, "dt_bias"), _ptr(a_log, torch.float32, "A_log"),
+                                    _ptr(d_skip, torch.float32, "D"), c_int(groups), c_int(_recurrence_warps(batch, heads, v)),
+                                    c_int(dtype_code(conv)), _stream()))
+    _launched()
+
+
+def recurrence_gate(q, f, v, f_bias, lower, state, out, batch, slots, heads, k, vdim):
+    """Per head S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T silu(q_t), f = lower + (1 - lower) sigmoid(raw + bias):
+    ``q`` and ``f`` [tokens, heads * k] raw projections, ``v`` [tokens, heads * vdim] (columns of wider rows allowed),
+    ``state`` float32 [slots, heads, k, vdim], ``out`` float32 [tokens, heads * vdim]."""
+    lib = kernels_library()
+    n = q.shape[0]
+    if q.shape != (n, heads * k) or f.shape != (n, heads * k) or v.shape != (n, heads * vdim) or out.shape != (n, heads * vdim) \
+            or state.shape[1:] != (heads, k, vdim) or f.dtype != q.dtype or v.dtype != q.dtype:
+        raise KernelError("recurrence_gate: shapes do not fit")
+    p0, l0 = _cols(q, "q")
+    p1, l1 = _cols(f, "f")
+    p2, l2 = _cols(v, "v")
+    check(lib.rmx_linear_recurrence(c_int(1), _ptr(state, torch.float32, "state"), _ptr(out, torch.float32, "out"),
+                                    _ptr(batch.q_start, torch.int32, "q_start"), _ptr(slots, torch.int32, "slots"), c_int(batch.n_seqs),
+                                    c_int(heads), c_int(k), c_int(vdim), p0, l0, p1, l1, p2, l2,
+                                    _ptr(f_bias, torch.float32, "f_bias"), _ptr(lower, torch.float32, "lower"), c_void_p(0), c_int(1),
+                                    c_int(_recurrence_warps(batch, heads, vdim)), c_int(dtype_code(q)), _stream()))
+    _launched()
+
+
+def group_rmsnorm(y, weight, eps, out, groups, gate=None, out_scale=1.0):
+    """out = RMSNorm of each of a row's ``groups`` equal parts of u = y (* silu(gate)), times ``weight`` (as long as a row,
+    or as long as a part and shared by the parts), times ``out_scale``; y float32, out and gate in the compute dtype."""
+    lib = kernels_library()
+    n, total = y.shape
+    if total % groups or out.shape != (n, total) or out.stride(1) != 1 or weight.numel() not in (total, total // groups) \
+            or (gate is not None and (gate.shape != (n, total) or gate.stride(1) != 1 or gate.dtype != out.dtype)):
+        raise KernelError("group_rmsnorm: shapes or dtypes do not fit")
+    check(lib.rmx_group_rmsnorm(_ptr(y, torch.float32, "y"), c_void_p(gate.data_ptr() if gate is not None else 0),
+                                c_int(gate.stride(0) if gate is not None else 0), _ptr(weight, torch.float32, "weight"),
+                                c_int(weight.numel()), c_float(eps), c_void_p(out.data_ptr()), c_int(out.stride(0)), c_int(n),
+                                c_int(groups), c_int(total // groups), c_float(out_scale), c_int(dtype_code(out)), _stream()))
     _launched()
 
 
@@ -849,12 +977,16 @@ class Kernels:
         return attention_flash(*args, **kwargs)
 
     def attention(self, q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace=None,
-                  projection=None):
+                  projection=None, sinks=None):
         """Picks the attention kernel for the dtype, head size and shape of the step.  A step that mixes decoded
         tokens with prompt portions runs as two launches, each kind with the kernel made for it.  ``projection``
         (see ``decode_takes_projection``): the q/k/v rows before norm and rotation, which the decoding kernel then
         finishes itself; ``q`` is not read."""
         group = nq // nkv
+        if sinks is not None:
+            attention_plain(q, k_pool, v_pool, batch.positions, batch.seq_index, block_table, page_size, out, nq, nkv, hd,
+                            window, scale, batch.status, sinks)
+            return
         if projection is not None:
             self.attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace,
                                  projection=projection)

@@ -112,3 +112,100 @@ class AttentionMixer(Mixer):
         if self.b_o is not None:
             ops.add_bias(y, self.b_o)
         return y
+
+
+class GatedAttentionMixer(Mixer):
+    """Grouped-query attention with the options some designs add to it, each a parameter:
+
+    ``dim`` / ``vdim``: query/key and value heads of different sizes (the cache's heads take the larger, the rest is zeros);
+    ``whole_norm_eps``: q and k are RMS-normed over the WHOLE projection, all heads at once, with weights of the
+        projection's size, before they are split into heads and rotated (None: no norm);
+    ``sink``: the softmax's denominator has one more term, exp(0): p_j = exp(s_j) / (1 + sum_j exp(s_j)), a key that every
+        query may give weight to and that has no value;
+    ``gate``: the concatenated heads are multiplied with sigmoid(W_g x), number by number, before the output product;
+    ``scale``: of the scores; ``position``: the rotation (over the first ``rotary_dim`` numbers of a head, halves paired).
+
+    The four products that read the layer's input (q, k, v, gate) are one product over stacked weights.
+    """
+
+    graph_safe = True
+    NAMES = {"q": "q", "k": "k", "v": "v", "o": "o", "g": "g", "q_norm": "q.norm", "k_norm": "k.norm"}
+
+    def __init__(self, prefix: str, width: int, heads: int, kv_heads: int, dim: int, vdim: int, position, scale: float,
+                 whole_norm_eps: float | None = None, sink: bool = False, gate: bool = False, window: int = 0,
+                 names: dict | None = None, out_name: str = "mixer_out"):
+        if heads % kv_heads:
+            raise ValueError("heads must be a multiple of kv_heads")
+        self.prefix, self.width = prefix, int(width)
+        self.heads, self.kv_heads, self.dim, self.vdim = int(heads), int(kv_heads), int(dim), int(vdim)
+        self.head_dim = max(self.dim, self.vdim)     # of the cache, of q as the attention kernels read it, and of their output
+        self.position = position
+        self.scale = float(scale) * float(getattr(position, "score_scale", 1.0))
+        self.whole_norm_eps, self.sink, self.gate, self.window = whole_norm_eps, bool(sink), bool(gate), int(window)
+        self.names = {k: f"{prefix}.{v}" for k, v in {**self.NAMES, **(names or {})}.items()}
+        self.out_name = out_name
+        self.q_norm = self.k_norm = self.sinks = None
+
+    def children(self):
+        return [self.position]
+
+    def cache_spec(self):
+        return CacheSpec("paged", kv_heads=self.kv_heads, head_dim=self.head_dim, window=self.window)
+
+    def graph_key(self, shape):
+        return (self.ctx.ops.decode_attention_splits(shape.n_seqs, self.kv_heads, self.head_dim, self.heads // self.kv_heads,
+                                                     shape.max_seq_len, self.ctx.dtype),)
+
+    def param_specs(self):
+        n, qd, kd = self.names, self.heads * self.dim, self.kv_heads * self.dim
+        specs = [ParamSpec(n["q"], (qd, self.width)), ParamSpec(n["k"], (kd, self.width)),
+                 ParamSpec(n["v"], (self.kv_heads * self.vdim, self.width)), ParamSpec(n["o"], (self.width, self.heads * self.vdim))]
+        if self.whole_norm_eps is not None:
+            specs += [ParamSpec(n["q_norm"], (qd,), "norm", "float32"), ParamSpec(n["k_norm"], (kd,), "norm", "float32")]
+        if self.gate:
+            specs.append(ParamSpec(n["g"], (self.heads * self.vdim, self.width)))
+        return specs
+
+    def bind(self, tensors, ctx):
+        super().bind(tensors, ctx)
+        n = self.names
+        stack = [tensors.pop(n["q"]), tensors.pop(n["k"]), tensors.pop(n["v"])] + ([tensors.pop(n["g"])] if self.gate else [])
+        self.w_in = torch.cat(stack, dim=0).contiguous()
+        self.w_o = tensors[n["o"]].contiguous()
+        if self.whole_norm_eps is not None:
+            self.q_norm, self.k_norm = tensors[n["q_norm"]].contiguous(), tensors[n["k_norm"]].contiguous()
+        if self.sink:
+            self.sinks = torch.zeros(self.heads, dtype=torch.float32, device=ctx.device)
+
+    def linear_weights(self):
+        return [self.w_in, self.w_o]
+
+    def forward(self, x, batch, cache):
+        ops, ws, dt = self.ctx.ops, self.ctx.workspace, self.ctx.dtype
+        n, nq, nkv, hd = x.shape[0], self.heads, self.kv_heads, self.head_dim
+        proj = ws.get("qkvg", (n, self.w_in.shape[0]), dt)
+        ops.linear(x, self.w_in, proj, ws, batch.status)
+        tap = self.ctx.tap
+        if tap is not None:
+            tap("qkv", proj)
+        q = ws.get("q_rot", (n, nq * hd), dt)
+        ops.qk_whole_norm_rope_cache(proj, self.q_norm, self.k_norm, self.whole_norm_eps or 0.0, self.position.inv_freq,
+                                     self.position.rotary_dim, batch.positions, batch.seq_index, cache.block_table, cache.page_size,
+                                     cache.k_pool, cache.v_pool, q, nq, nkv, self.dim, self.vdim, hd, not cache.read_only,
+                                     batch.status, self.position.angles(batch))
+        if tap is not None:
+            tap("q_rot", q)
+        o = ws.get("attn_out", (n, nq * hd), dt)
+        ops.attention(q, cache.k_pool, cache.v_pool, batch, cache.block_table, cache.page_size, o, nq, nkv, hd, cache.window,
+                      self.scale, ws, sinks=self.sinks)
+        if tap is not None:
+            tap("attn_out", o)
+        if self.gate:
+            gated = o if hd == self.vdim else ws.get("attn_gated", (n, nq * self.vdim), dt)
+            ops.sigmoid_gate(o, hd, proj[:, (nq + nkv) * self.dim + nkv * self.vdim:], gated, nq, self.vdim)
+            o = gated
+        elif hd != self.vdim:
+            o = o.view(n, nq, hd)[:, :, :self.vdim].reshape(n, nq * self.vdim)
+        y = ws.get(self.out_name, (n, self.width), dt)
+        ops.linear(o, self.w_o, y, ws, batch.status)
+        return y

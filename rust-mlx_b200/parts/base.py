@@ -47,7 +47,8 @@ class CacheSpec:
     pages; ``window`` > 0 means only the last ``window`` positions are ever read, so
     older pages can be given back.  ``values=False``: one pool only (a mixer that keeps a
     single latent per token, from which it forms keys and values alike).  kind "state": ``state_shape`` numbers of
-    ``state_dtype`` per request, of fixed size, zero when a request starts.
+    ``state_dtype`` ("float32", "bfloat16", "int32", or "compute": the run's dtype) per request, of fixed size, zero when a
+    request starts.
     Layers with equal specs share a cache group (one page pool geometry, one block
     table per request).
     """
@@ -92,13 +93,22 @@ class DecodeShape:
 
 @dataclass
 class ScaledSum:
-    """What a block leaves to be added to the residual stream when it is not one tensor: factor * (first + second),
+    """What a block leaves to be added to the residual stream when it is not one tensor: factor * (first + ratio * second),
     formed in float by the norm that adds it (``second`` may be None).  A block whose mixer and feed-forward read
-    the same normed rows hands both outputs on like this."""
+    the same normed rows hands both outputs on like this; so does a mixer of two mixers side by side, each with a
+    factor of its own (``weighted``)."""
 
     first: torch.Tensor
     second: Optional[torch.Tensor] = None
     factor: float = 1.0
+    ratio: float = 1.0
+
+    @staticmethod
+    def weighted(a, wa: float, b, wb: float) -> "ScaledSum":
+        """wa * a + wb * b."""
+        if wa == 0.0:
+            return ScaledSum(b, a, wb, 0.0)
+        return ScaledSum(a, b, wa, wb / wa)
 
 
 class Part:

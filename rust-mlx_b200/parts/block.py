@@ -13,16 +13,23 @@ from .base import Part, ScaledSum
 
 
 class PreNormBlock(Part):
+    """``norm2`` and ``ffn`` may both be None (a layer of a mixer alone: what the mixer gives is the block's pending
+    delta).  ``input_conv`` (a ``ShortConv`` with ``residual``): what the mixer reads is x + conv(x) of the normed rows,
+    a short causal convolution over time whose last inputs are part of every request's state; it is the first thing the
+    block remembers, before what its mixer remembers."""
+
     graph_safe = True
 
-    def __init__(self, norm1, mixer, norm2, ffn):
-        self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
+    def __init__(self, norm1, mixer, norm2=None, ffn=None, input_conv=None):
+        if (norm2 is None) != (ffn is None):
+            raise ValueError("a block has a second norm exactly when it has a feed-forward")
+        self.norm1, self.mixer, self.norm2, self.ffn, self.input_conv = norm1, mixer, norm2, ffn, input_conv
 
     def children(self):
-        return [self.norm1, self.mixer, self.norm2, self.ffn]
+        return [p for p in (self.norm1, self.input_conv, self.mixer, self.norm2, self.ffn) if p is not None]
 
     def cache_specs(self):
-        return self.mixer.cache_specs()
+        return (self.input_conv.cache_specs() if self.input_conv is not None else []) + self.mixer.cache_specs()
 
     def forward(self, h, pending, batch, cache):
         tap = self.ctx.tap
@@ -30,9 +37,17 @@ class PreNormBlock(Part):
         if tap is not None:
             tap("residual", h)      # the stream as this block finds it: everything before it has been added
             tap("norm1", x)
+        if self.input_conv is not None:
+            views = list(cache) if isinstance(cache, (tuple, list)) else [cache]
+            x = self.input_conv.forward(x, batch, views[0], self.ctx.workspace.get("conv_in", tuple(x.shape), x.dtype))
+            cache = None if len(views) == 1 else (views[1] if len(views) == 2 else tuple(views[1:]))
+            if tap is not None:
+                tap("conv_in", x)
         a = self.mixer.forward(x, batch, cache)
-        if tap is not None:
+        if tap is not None and not isinstance(a, ScaledSum):
             tap("mixer_out", a)
+        if self.ffn is None:
+            return h, a
         h, x = self.norm2.forward(h, a)
         if tap is not None:
             tap("norm2", x)

@@ -14,9 +14,10 @@ from .base import ParamSpec, Part
 class TokenEmbedding(Part):
     graph_safe = True
 
-    def __init__(self, name: str, vocab: int, width: int):
+    def __init__(self, name: str, vocab: int, width: int, scale: float = 1.0):
         self.name, self.vocab, self.width = name, int(vocab), int(width)
-        self.weight = None
+        self.scale = float(scale)   # a token's row is multiplied with this on its way into the stream (in float); a head
+        self.weight = None          # tied to this table reads it unscaled
 
     def param_specs(self):
         return [ParamSpec(self.name, (self.vocab, self.width), "embedding")]
@@ -30,9 +31,10 @@ class TokenEmbedding(Part):
         step's sampling left on the device for its sequence."""
         h = self.ctx.workspace.get("residual", (ids.shape[0], self.width), torch.float32)
         if batch is not None and batch.last_tokens is not None:
-            self.ctx.ops.embedding(ids, self.weight, h, batch.from_last, batch.seq_index, batch.slots, batch.last_tokens)
+            self.ctx.ops.embedding(ids, self.weight, h, batch.from_last, batch.seq_index, batch.slots, batch.last_tokens,
+                                   scale=self.scale)
         else:
-            self.ctx.ops.embedding(ids, self.weight, h)
+            self.ctx.ops.embedding(ids, self.weight, h, scale=self.scale)
         return h
 
 

@@ -12,10 +12,10 @@ from .base import Norm, ParamSpec, ScaledSum
 
 
 def _terms(delta):
-    """(first, second, factor) of what is to be added to the stream."""
+    """(first, second, factor, ratio) of what is to be added to the stream: factor * (first + ratio * second)."""
     if isinstance(delta, ScaledSum):
-        return delta.first, delta.second, delta.factor
-    return delta, None, 1.0
+        return delta.first, delta.second, delta.factor, delta.ratio
+    return delta, None, 1.0, 1.0
 
 
 class RMSNorm(Norm):
@@ -34,12 +34,12 @@ class RMSNorm(Norm):
 
     def forward(self, h, delta):
         x = self.ctx.workspace.get("norm_out", (h.shape[0], self.width), self.ctx.dtype)
-        first, second, factor = _terms(delta)
-        self.ctx.ops.add_rmsnorm(h, first, self.weight, self.eps, x, delta2=second, mult=factor)
+        first, second, factor, ratio = _terms(delta)
+        self.ctx.ops.add_rmsnorm(h, first, self.weight, self.eps, x, delta2=second, mult=factor, mult2=ratio)
         return h, x
 
     def forward_rows(self, h, delta, rows):
         x = self.ctx.workspace.get("norm_rows_out", (rows.shape[0], self.width), self.ctx.dtype)
-        first, second, factor = _terms(delta)
-        self.ctx.ops.add_rmsnorm(h, first, self.weight, self.eps, x, rows=rows, delta2=second, mult=factor)
+        first, second, factor, ratio = _terms(delta)
+        self.ctx.ops.add_rmsnorm(h, first, self.weight, self.eps, x, rows=rows, delta2=second, mult=factor, mult2=ratio)
         return x
