@@ -80,7 +80,9 @@ class CachePools:
             if grp.spec.kind == "paged":
                 grp.table_index = len(geometry)
                 geometry.append(GroupGeometry(num_pages, self.page_size, grp.spec.window))
-                shape = (n, num_pages, grp.spec.kv_heads, self.page_size, grp.spec.head_dim)
+                # (one page more than the page table deals out: the spare places of a padded decode graph write there when
+                # what they compute may differ from the sequence they repeat)
+                shape = (n, num_pages + 1, grp.spec.kv_heads, self.page_size, grp.spec.head_dim)
                 grp.k_pool = torch.zeros(shape, dtype=dtype, device=device)
                 grp.v_pool = torch.zeros(shape, dtype=dtype, device=device) if grp.spec.values else None
             elif grp.spec.kind == "state":

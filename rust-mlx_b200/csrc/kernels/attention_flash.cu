@@ -81,7 +81,25 @@ struct FlashParams {
     __nv_bfloat16* v_store;
     float eps;
     int qkv_stride;
+    const float* sinks;            // [nq] or null: a score a query head that enters the softmax's denominator and has no value
 };
+
+// A sink: one more term exp(sink) in a row's denominator, with no value.  It is added to ONE of the partial results of a
+// row (the first key split's, and there the first warp's) before partial results are combined, so that every way of
+// combining them stays as it is.  m is in base-2 units, as the scores are.
+template <int DTILES>
+__device__ __forceinline__ void add_sink(float sink, float (&o)[DTILES][4], float& m, float& l, int i) {
+    const float sk = sink * LOG2E;
+    const float m_new = fmaxf(m, sk);
+    const float corr = m == -INFINITY ? 0.f : exp2f(m - m_new);
+    l = l * corr + exp2f(sk - m_new);
+    m = m_new;
+#pragma unroll
+    for (int d = 0; d < DTILES; ++d) {
+        o[d][2 * i] *= corr;
+        o[d][2 * i + 1] *= corr;
+    }
+}
 
 template <int HD, bool KEYSPLIT>
 __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashParams p) {
@@ -315,6 +333,13 @@ __global__ void __launch_bounds__(THREADS) attention_flash_kernel(const FlashPar
     for (int i = 0; i < 2; ++i) {
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+    }
+    if (p.sinks != nullptr && split == 0 && (!KEYSPLIT || warp == 0)) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int r = KEYSPLIT ? (lane >> 2) + 8 * i : (i == 0 ? r_lo : r_hi);
+            add_sink<DTILES>(p.sinks[kvh * p.group + r % p.group], o, m[i], l[i], i);
+        }
     }
     if constexpr (KEYSPLIT) {
         // the four warps hold partial results for the same rows: combine them in warp order
@@ -781,6 +806,13 @@ __global__ void __launch_bounds__(DTHREADS, 2) attention_tma_kernel(const __grid
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
     }
     if (tid == 0 && s_failed) atomicExch(p.status, 3);
+    if (p.sinks != nullptr && split == 0 && (!KEYSPLIT || warp == 0)) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int r = KEYSPLIT ? (lane >> 2) + 8 * i : row_base + (lane >> 2) + 8 * i;
+            add_sink<DTILES>(p.sinks[kvh * p.group + r % p.group], o, m[i], l[i], i);
+        }
+    }
 
     if constexpr (!KEYSPLIT) {
         if (!warp_active) return;
@@ -1163,8 +1195,8 @@ RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v
                                 void* out, float* part_o, float* part_ml, unsigned int* counters, int n_seqs, int n_tokens, int n_tiles,
                                 int nq, int nkv, int hd, int window, float scale, int n_splits, int max_q_len,
                                 int pool_pages, const void* qkv, int qkv_stride, const float* q_norm, const float* k_norm,
-                                float eps, const float* cos_sin, int write_kv, int first_token, int run_tokens, int* status,
-                                void* stream) {
+                                float eps, const float* cos_sin, int write_kv, int first_token, int run_tokens, const float* sinks,
+                                int* status, void* stream) {
     if (n_tokens == 0) return 0;
     // first_token, run_tokens: the tokens of the sequences given here (a step's sequences may be given in several
     // calls, each with a run of them; q, out and the partial sums are those of the whole step)
@@ -1181,6 +1213,7 @@ RMX_API int rmx_attention_flash(const void* q, const void* k_pool, const void* v
     p.q = (const __nv_bfloat16*)q; p.k_pool = (const __nv_bfloat16*)k_pool; p.v_pool = (const __nv_bfloat16*)v_pool;
     p.q_start = q_start; p.positions = positions; p.block_table = block_table; p.out = (__nv_bfloat16*)out;
     p.part_o = part_o; p.part_ml = part_ml; p.status = status; p.counters = nullptr; p.cluster = 0;
+    p.sinks = sinks;
     p.qkv = (const __nv_bfloat16*)qkv; p.qkv_stride = qkv_stride; p.q_norm = q_norm; p.k_norm = k_norm; p.eps = eps; p.cos_sin = cos_sin;
     p.k_store = qkv && write_kv ? (__nv_bfloat16*)const_cast<void*>(k_pool) : nullptr;
     p.v_store = qkv && write_kv ? (__nv_bfloat16*)const_cast<void*>(v_pool) : nullptr;

@@ -221,6 +221,7 @@ struct Params {
     int n_splits, n_rows;          // n_rows = tokens * nq
     float* part_o;                 // [n_splits][n_rows][HD]
     float* part_ml;                // [n_splits][n_rows][2]
+    const float* sinks;            // [nq] or null: a score a query head that enters the softmax's denominator and has no value
 };
 
 // One block: two neighbouring query tiles (A and B, 128 rows each) of one sequence against one kv head.  Both use
@@ -698,6 +699,9 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
             fence_after();
             const int g = r - tok * p.group;
             const size_t row = (size_t)(tile_tok0 + tok) * p.nq + kvh * p.group + g;
+            // a sink: one more term in the row's sum, relative to the same reference as the others, in the first run's share
+            // (a sum that overflows to infinity gives the zeros that it should)
+            if (p.sinks != nullptr && blockIdx.z == 0 && n_kt > 0) l += exp2f(p.sinks[kvh * p.group + g] * LOG2E - m);
             if (p.n_splits > 1) {
                 // this run's share of the row (a run without keys leaves maximum -inf and sum 0, and no numbers)
                 float* dst = p.part_o + ((size_t)blockIdx.z * p.n_rows + row) * HD;
@@ -899,7 +903,7 @@ RMX_API int rmx_attention_tcgen05(const void* q, const void* k_pool, const void*
                                   const int* positions, const int* block_table, int table_stride, int page_size,
                                   void* out, int n_seqs, int n_tokens, int n_tiles, int tiles_per_block, int nq, int nkv,
                                   int hd, int window, float scale, int pool_pages, int n_splits, float* part_o, float* part_ml,
-                                  int first_token, int run_tokens, int* status, void* stream) {
+                                  int first_token, int run_tokens, const float* sinks, int* status, void* stream) {
     if (n_tokens == 0) return 0;
     RMX_REQUIRE(tiles_per_block == 1 || tiles_per_block == 2, "attention_tcgen05: a block takes 1 or 2 tiles, not %d", tiles_per_block);
     RMX_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_tcgen05: %d query heads over %d kv heads", nq, nkv);
@@ -917,7 +921,7 @@ RMX_API int rmx_attention_tcgen05(const void* q, const void* k_pool, const void*
     p.page_size = page_size; p.window = window; p.box_rows = page_size < BN ? page_size : BN;
     p.per_block = tiles_per_block;
     RMX_REQUIRE(n_splits >= 1 && n_splits <= 64 && (n_splits == 1 || (part_o && part_ml)), "attention_tcgen05: %d runs of keys need room for their shares", n_splits);
-    p.n_splits = n_splits; p.n_rows = n_tokens * nq; p.part_o = part_o; p.part_ml = part_ml;
+    p.n_splits = n_splits; p.n_rows = n_tokens * nq; p.part_o = part_o; p.part_ml = part_ml; p.sinks = sinks;
     p.page_shift = 0;
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.scale_log2 = scale * LOG2E;

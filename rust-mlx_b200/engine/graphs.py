@@ -83,6 +83,7 @@ class DecodeGraphs:
         event.synchronize()
         facts = cap.layout.fill(host.numpy(), seqs, e.pools, e.vocab_size, temperatures, uniforms)
         cap.layout.part(host.numpy(), 10)[n_real:] = e.pools.max_requests
+        self._spare_tables(cap.layout, host.numpy(), n_real)
         cap.batch.max_seq_len = facts["max_seq_len"]
         cap.dev.copy_(host, non_blocking=True)
         event.record()
@@ -105,6 +106,7 @@ class DecodeGraphs:
         cap.result = torch.zeros(n + 1, dtype=torch.int32, device=e.device)
         facts = cap.layout.fill(cap.hosts[0].numpy(), seqs, e.pools, e.vocab_size, temperatures, uniforms)
         cap.layout.part(cap.hosts[0].numpy(), 10)[n if n_real is None else n_real:] = e.pools.max_requests
+        self._spare_tables(cap.layout, cap.hosts[0].numpy(), n if n_real is None else n_real)
         cap.dev.copy_(cap.hosts[0], non_blocking=True)
         cap.events[0].record()
         cap.batch = cap.layout.views(cap.dev, e._status, facts)
@@ -146,6 +148,16 @@ class DecodeGraphs:
         self.graphs[key] = cap
         self.captures += 1
         return cap
+
+    def _spare_tables(self, layout, buf, n_real: int) -> None:
+        """In a model that keeps states of fixed size a spare place steps the slot that belongs to no request, so what it
+        computes is not what the sequence it repeats computes: its keys and values must not land in that sequence's
+        pages.  Every entry of its block tables names the page that belongs to no request."""
+        pools = self.engine.pools
+        if not pools.state_groups or n_real >= layout.n_seqs:
+            return
+        for g in range(len(pools.paged_groups)):
+            layout.part(buf, layout.first_table + g).reshape(layout.n_seqs, layout.entries[g])[n_real:] = pools.num_pages
 
     def _step(self, cap) -> None:
         e = self.engine

@@ -574,7 +574,7 @@ def flash_takes_projection(hd: int, group: int, page_size: int, rotary_dim: int)
 
 
 def attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace,
-                    n_splits=None, projection=None, use_tma=True):
+                    n_splits=None, projection=None, use_tma=True, sinks=None):
     """Tensor-core attention over pages for bfloat16 (prompt portions and decoded tokens alike).  ``projection``:
     (qkv rows, q_norm, k_norm, eps, cos_sin, write_kv) for a decoding step whose kernel finishes the projection.
     ``use_tma``: keys and values are fetched by TMA where the kernel is built for it."""
@@ -602,7 +602,8 @@ def attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, n
         c_int(getattr(batch, "max_q_len", 0)), c_int(k_pool.shape[0] if use_tma else 0),
         _ptr(qkv, torch.bfloat16, "qkv"), c_int(qkv.stride(0) if qkv is not None else 0), _ptr(q_norm, torch.float32, "q_norm"),
         _ptr(k_norm, torch.float32, "k_norm"), c_float(eps), _ptr(cos_sin, torch.float32, "cos_sin"), c_int(1 if write_kv else 0),
-        c_int(starts[0]), c_int(starts[batch.n_seqs] - starts[0]), _ptr(batch.status, torch.int32, "status"), _stream()))
+        c_int(starts[0]), c_int(starts[batch.n_seqs] - starts[0]), _ptr(sinks, torch.float32, "sinks"),
+        _ptr(batch.status, torch.int32, "status"), _stream()))
     _launched(2 if n_splits > 1 else 1)
 
 
@@ -734,7 +735,7 @@ def tcgen05_attention_shape(counts: list, nkv: int, group: int, max_seq_len: int
 
 
 def attention_tcgen05(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, per_block=None,
-                      n_splits=None, workspace=None):
+                      n_splits=None, workspace=None, sinks=None):
     """Prompt portions: S = Q K^T and O += P V as tcgen05 MMAs with accumulators in tensor memory (see
     ``tcgen05_attention_shape`` for how the work is divided; ``per_block`` and ``n_splits`` override it)."""
     lib = kernels_library()
@@ -759,7 +760,8 @@ def attention_tcgen05(q, k_pool, v_pool, batch, block_table, page_size, out, nq,
         _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), c_int(page_size),
         _ptr(out, torch.bfloat16, "out"), c_int(batch.n_seqs), c_int(q.shape[0]), c_int(n_tiles), c_int(per_block),
         c_int(nq), c_int(nkv), c_int(hd), c_int(window), c_float(scale), c_int(k_pool.shape[0]), c_int(n_splits),
-        _ptr(part_o), _ptr(part_ml), c_int(starts[0]), c_int(starts[-1] - starts[0]), _ptr(batch.status, torch.int32, "status"), _stream()))
+        _ptr(part_o), _ptr(part_ml), c_int(starts[0]), c_int(starts[-1] - starts[0]), _ptr(sinks, torch.float32, "sinks"),
+        _ptr(batch.status, torch.int32, "status"), _stream()))
     _launched(2 if n_splits > 1 else 1)
 
 
@@ -983,10 +985,6 @@ class Kernels:
         (see ``decode_takes_projection``): the q/k/v rows before norm and rotation, which the decoding kernel then
         finishes itself; ``q`` is not read."""
         group = nq // nkv
-        if sinks is not None:
-            attention_plain(q, k_pool, v_pool, batch.positions, batch.seq_index, block_table, page_size, out, nq, nkv, hd,
-                            window, scale, batch.status, sinks)
-            return
         if projection is not None:
             self.attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace,
                                  projection=projection)
@@ -996,21 +994,24 @@ class Kernels:
             if runs is not None:
                 for run in runs:
                     self._attention_bf16(q, k_pool, v_pool, run, block_table[run.first:run.last], page_size, out, nq, nkv, hd,
-                                         window, scale, workspace)
+                                         window, scale, workspace, sinks)
                 return
-        self._attention_bf16(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace)
+        self._attention_bf16(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace, sinks)
 
-    def _attention_bf16(self, q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace):
+    def _attention_bf16(self, q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace,
+                        sinks=None):
         group = nq // nkv
         if (q.dtype == torch.bfloat16 and self.use_tcgen05_attention and getattr(batch, "max_q_len", 0) * group > 16
                 and tcgen05_attention_supported(hd, group, page_size)):
-            attention_tcgen05(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace=workspace)
+            attention_tcgen05(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace=workspace,
+                              sinks=sinks)
             return
         if q.dtype == torch.bfloat16 and workspace is not None and flash_supported(hd, nq // nkv):
-            self.attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace)
+            self.attention_flash(q, k_pool, v_pool, batch, block_table, page_size, out, nq, nkv, hd, window, scale, workspace,
+                                 sinks=sinks)
             return
         attention_plain(q, k_pool, v_pool, batch.positions, batch.seq_index, block_table, page_size, out, nq, nkv, hd,
-                        window, scale, batch.status)
+                        window, scale, batch.status, sinks)
 
     def decode_attention_splits(self, n_seqs: int, nkv: int, hd: int, group: int, max_seq_len: int, dtype) -> int:
         """How many blocks share the keys of a (sequence, kv head) when ``n_seqs`` sequences decode one token each:

@@ -156,7 +156,8 @@ def forward(config, tensors, tokens, layers_out=None):
     for i, layer in enumerate(config["layers"]):
         p = f"l{i}"
         h = rms(x, eps) * t[f"{p}.norm1"]
-        h = h + causal_conv(h, t[f"{p}.canon1"])
+        if config.get("canon"):                      # (a model without the key has no input convolution)
+            h = h + causal_conv(h, t[f"{p}.canon1"])
         if layer["type"] == "mamba2":
             x = x + mamba2(h, t, f"{p}.mix", layer["mixer"], eps)
         elif layer["type"] == "parallel":
@@ -165,10 +166,6 @@ def forward(config, tensors, tokens, layers_out=None):
             raise ValueError(f"unknown mixer {layer['type']!r}")
         if layer.get("mlp") is not None:
             x = x + feed_forward(rms(x, eps) * t[f"{p}.norm2"], t, f"{p}.mlp")
-        if layer_out_wanted(layers_out):
+        if layers_out is not None:
             layers_out.append(x.clone())
     return (rms(x, eps) * t["final.norm"]) @ t["embed"].T
-
-
-def layer_out_wanted(layers_out) -> bool:
-    return layers_out is not None
