@@ -397,6 +397,80 @@ FAMILY_SIZES = {
 }
 
 
+# --family gugalorn: the Gugalorn design (state-space layers and layers of softmax attention beside gated linear attention)
+# at layer sizes of real models, beside the Qwen3 dense decoder of equal width, depth, heads and feed-forward width.
+
+def gugalorn_shape(width, heads, kv_heads, dim, rot, ssm_heads, ssm_vdim, state, ssm_groups, gla_heads, gla_dim, gla_vdim, ff, vocab,
+                   groups=1):
+    """Groups of four layers: a state-space layer without a feed-forward, two parallel layers with one, a state-space layer."""
+    ssm = {"type": "mamba2", "mixer": {"heads": ssm_heads, "vdim": ssm_vdim, "state": state, "groups": ssm_groups, "conv": 4,
+                                       "norm_groups": ssm_groups}, "mlp": None}
+    par = {"type": "parallel",
+           "mixer": {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "rot": {"dims": rot, "base": 1e6}, "scale": dim ** -0.5},
+                     "right": {"heads": gla_heads, "dim": gla_dim, "vdim": gla_vdim}, "left_scale": 1.0, "right_scale": 1.0},
+           "mlp": {"kind": "dense", "ff": ff}}
+    return {"architecture": "Gugalorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "canon": {"taps": 4}, "layers": [ssm, par, par, ssm] * groups}
+
+
+GUGALORN_SIZES = {
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=64, rot=32, ssm_heads=64, ssm_vdim=64, state=128, ssm_groups=8, gla_heads=16,
+               gla_dim=128, gla_vdim=128, ff=8192, vocab=32768),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, rot=64, ssm_heads=128, ssm_vdim=64, state=128, ssm_groups=8, gla_heads=32,
+               gla_dim=128, gla_vdim=128, ff=12288, vocab=65536),
+}
+
+
+def gugalorn_costs(raw, starts, counts):
+    """tap name -> function(layer) -> (bytes, flops on the tensor cores) of the kernels that end at that tap."""
+    n, W, S = sum(counts), raw["width"], len(counts)
+    cached = sum(s + c for s, c in zip(starts, counts))
+
+    def ssm(f):
+        m = f["mixer"]
+        inner = m["heads"] * m["vdim"]
+        return m, inner, inner + 2 * m["groups"] * m["state"]
+
+    def left(f):
+        a = f["mixer"]["left"]
+        return a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+
+    def right(f):
+        g = f["mixer"]["right"]
+        return g["heads"] * g["dim"], g["heads"] * g["vdim"], g["heads"] * g["dim"] * g["vdim"]
+
+    return {
+        "norm1": lambda f: (n * W * 12.0, 0.0), "norm2": lambda f: (n * W * 12.0, 0.0),
+        "conv_in": lambda f: (n * W * 4.0, 0.0),
+        "ssm_in": lambda f: _product(n, 2 * ssm(f)[1] + 2 * ssm(f)[0]["groups"] * ssm(f)[0]["state"] + ssm(f)[0]["heads"], W),
+        "ssm_conv": lambda f: (4.0 * n * ssm(f)[2], 0.0),
+        "recurrence_out": lambda f: (2.0 * n * ssm(f)[2] + 4.0 * n * ssm(f)[1] + 8.0 * S * ssm(f)[1] * ssm(f)[0]["state"], 0.0),
+        "recurrence_normed": lambda f: (8.0 * n * ssm(f)[1], 0.0),
+        "mixer_out": lambda f: _product(n, W, ssm(f)[1]),
+        "qkv": lambda f: _product(n, (left(f)[0] + left(f)[1]) * (left(f)[2] + left(f)[3]), W),
+        "q_rot": lambda f: (4.0 * n * (left(f)[0] + 2 * left(f)[1]) * left(f)[2], 0.0),
+        "attn_out": lambda f: (4.0 * cached * left(f)[1] * left(f)[2] + 4.0 * n * left(f)[0] * left(f)[2],
+                               4.0 * _keys_seen(starts, counts, 0) * left(f)[0] * left(f)[2]),
+        "attn_gated": lambda f: (6.0 * n * left(f)[0] * left(f)[3], 0.0),
+        "attn_proj": lambda f: _product(n, W, left(f)[0] * left(f)[3]),
+        "gla_in": lambda f: _product(n, 2 * right(f)[0] + right(f)[1], W),
+        "gla_recurrence_out": lambda f: (2.0 * n * (2 * right(f)[0] + right(f)[1]) + 4.0 * n * right(f)[1] + 8.0 * S * right(f)[2], 0.0),
+        "gla_normed": lambda f: (6.0 * n * right(f)[1], 0.0),
+        "gla_proj": lambda f: _product(n, W, right(f)[1]),
+        "ffn_act": lambda f: _product(n, 2 * f["mlp"]["ff"], W),
+        "ffn_out": lambda f: _product(n, W, f["mlp"]["ff"]),
+    }
+
+
+GUGALORN_PHASES = {"norm1": "add + norm", "norm2": "add + norm", "conv_in": "input convolution", "ssm_in": "state-space input product",
+                   "ssm_conv": "inner convolution + silu", "recurrence_out": "state-space recurrence",
+                   "recurrence_normed": "gate + group norm", "mixer_out": "state-space output product",
+                   "qkv": "q/k/v/gate product", "q_rot": "whole-projection norm + rotation + cache write", "attn_out": "attention with a sink",
+                   "attn_gated": "output gate", "attn_proj": "attention output product", "gla_in": "linear attention's q/f/v product",
+                   "gla_recurrence_out": "gated linear recurrence", "gla_normed": "norm a head", "gla_proj": "linear attention's output product",
+                   "ffn_act": "gate/up product + activation", "ffn_out": "down product"}
+
+
 def _product(n, rows, cols):
     """(bytes, flops) of [n, cols] . [rows, cols]^T in bfloat16."""
     return 2.0 * (rows * cols + n * cols + n * rows), 2.0 * n * rows * cols
@@ -557,27 +631,30 @@ def phase_table(engine, seqs, costs, names, layer_of, pk, reps, warmup):
     return rows, event_us
 
 
-def family_resolorn(a):
+def family_bench(a):
     """Decode (batch ``a.batch`` at context CONTEXT) and prefill (PREFILL_TOKENS tokens) of Resolorn layers beside Qwen3
     layers of equal width, depth, head size and feed-forward width, with every phase against its roofline."""
     import torch
-    from rust_mlx_b200.config import Qwen3Config, ResolornConfig
+    from rust_mlx_b200.config import GugalornConfig, Qwen3Config, ResolornConfig
     from rust_mlx_b200.engine import Engine
     from rust_mlx_b200.engine.batch import SequenceInput
     pk = peaks()
-    out = {"metric": "Resolorn beside Qwen3 at equal layer sizes: decode and prefill tok/s, phases against their rooflines", "impl": "ours",
+    gug = a.family == "gugalorn"
+    sizes = GUGALORN_SIZES if gug else FAMILY_SIZES
+    out = {"metric": f"{a.family.capitalize()} beside Qwen3 at equal layer sizes: decode and prefill tok/s, phases against their rooflines", "impl": "ours",
            "dtype": "bf16", "data": "synthetic", "n_gpus": 1, "batch": a.batch, "context": CONTEXT, "prefill_tokens": PREFILL_TOKENS,
            "peaks": pk, "sizes": {}}
-    for size in (a.family_size.split(",") if a.family_size else sorted(FAMILY_SIZES)):
-        s = FAMILY_SIZES[size]
+    for size in (a.family_size.split(",") if a.family_size else sorted(sizes)):
+        s = sizes[size]
         groups = max(1, a.family_layers // 4)
-        raw_r = resolorn_shape(groups=groups, **s)
+        raw_r = gugalorn_shape(groups=groups, **s) if gug else resolorn_shape(groups=groups, **s)
         raw_q = dict(QWEN3_8B, num_hidden_layers=4 * groups, hidden_size=s["width"], num_attention_heads=s["heads"],
-                     num_key_value_heads=max(1, s["heads"] // 4), head_dim=s["dim"], intermediate_size=s["ff"], vocab_size=s["vocab"],
-                     max_position_embeddings=2 * MAX_CONTEXT)
+                     num_key_value_heads=s["kv_heads"] if gug else max(1, s["heads"] // 4), head_dim=s["dim"],
+                     intermediate_size=s["ff"], vocab_size=s["vocab"], max_position_embeddings=2 * MAX_CONTEXT)
         result = {}
-        for family, raw, cfg, costs_of, names in (("resolorn", raw_r, ResolornConfig.from_dict(raw_r), resolorn_costs, RESOLORN_PHASES),
-                                                  ("qwen3", raw_q, Qwen3Config.from_dict(raw_q), qwen3_costs, QWEN3_PHASES)):
+        mine = ("gugalorn", raw_r, GugalornConfig.from_dict(raw_r), gugalorn_costs, GUGALORN_PHASES) if gug else \
+               ("resolorn", raw_r, ResolornConfig.from_dict(raw_r), resolorn_costs, RESOLORN_PHASES)
+        for family, raw, cfg, costs_of, names in (mine, ("qwen3", raw_q, Qwen3Config.from_dict(raw_q), qwen3_costs, QWEN3_PHASES)):
             cache_tokens = a.batch * (CONTEXT + 2 * PAGE + a.steps + a.warmup + 64) + 2 * PREFILL_TOKENS
             engine = Engine(cfg, dtype="bfloat16", random_weights=True, seed=0, max_tokens=cache_tokens, page_size=PAGE,
                             max_requests=a.batch + 4, tuning=a.policy)
@@ -587,7 +664,7 @@ def family_resolorn(a):
                     grp.v_pool.normal_(0, 1)
             ms, launches, clock_info = time_decode(engine, a.batch, a.steps, a.warmup, ClockSampler())
             pf_ms = time_prefill(engine, PREFILL_TOKENS)
-            layer_of = (lambda run, raw=raw: raw["layers"][run]) if family == "resolorn" else (lambda run: {})
+            layer_of = (lambda run, raw=raw: raw["layers"][run]) if family != "qwen3" else (lambda run: {})
             # phases of a decode step and of a prompt
             run = DecodeRun(engine, a.batch, CONTEXT)
             try:
@@ -647,7 +724,7 @@ def main():
     ap.add_argument("--continuous", action="store_true",
                     help="instead: 64 requests with prompts of 128..3072 random ids, 256 tokens each, through the "
                          "scheduler with chunked prefill of 512 (continuous batching); prints its own JSON line")
-    ap.add_argument("--family", default="", choices=["", "resolorn"],
+    ap.add_argument("--family", default="", choices=["", "resolorn", "gugalorn"],
                     help="instead: layers of this design at sizes of real models beside Qwen3 layers of equal width, depth, head "
                          "size and feed-forward width: decode and prefill tok/s and every phase against its roofline; prints its own "
                          "JSON line")
@@ -673,7 +750,7 @@ def main():
     CONTEXT = a.context
     if a.family:
         MAX_CONTEXT = max(MAX_CONTEXT, 2 * CONTEXT)
-        return family_resolorn(a)
+        return family_bench(a)
     base = SHAPES[a.shape]
     if a.shape != "qwen3-8b" and a.layers == QWEN3_8B["num_hidden_layers"]:
         a.layers = base["num_hidden_layers"]

@@ -701,7 +701,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tcgen05_kernel(const __g
             const size_t row = (size_t)(tile_tok0 + tok) * p.nq + kvh * p.group + g;
             // a sink: one more term in the row's sum, relative to the same reference as the others, in the first run's share
             // (a sum that overflows to infinity gives the zeros that it should)
-            if (p.sinks != nullptr && blockIdx.z == 0 && n_kt > 0) l += exp2f(p.sinks[kvh * p.group + g] * LOG2E - m);
+            if (p.sinks != nullptr && row_ok && blockIdx.z == 0 && n_kt > 0) l += exp2f(p.sinks[kvh * p.group + g] * LOG2E - m);   // (a row past the tile's last has no head)
             if (p.n_splits > 1) {
                 // this run's share of the row (a run without keys leaves maximum -inf and sum 0, and no numbers)
                 float* dst = p.part_o + ((size_t)blockIdx.z * p.n_rows + row) * HD;

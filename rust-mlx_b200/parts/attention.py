@@ -204,8 +204,12 @@ class GatedAttentionMixer(Mixer):
             gated = o if hd == self.vdim else ws.get("attn_gated", (n, nq * self.vdim), dt)
             ops.sigmoid_gate(o, hd, proj[:, (nq + nkv) * self.dim + nkv * self.vdim:], gated, nq, self.vdim)
             o = gated
+            if tap is not None:
+                tap("attn_gated", o)
         elif hd != self.vdim:
             o = o.view(n, nq, hd)[:, :, :self.vdim].reshape(n, nq * self.vdim)
         y = ws.get(self.out_name, (n, self.width), dt)
         ops.linear(o, self.w_o, y, ws, batch.status)
+        if tap is not None:
+            tap("attn_proj", y)
         return y

@@ -69,16 +69,22 @@ class StateSpaceMixer(Mixer):
         n, inner, cc = x.shape[0], self.inner, self.conv_channels
         proj = ws.get("ssm_in", (n, self.w_in.shape[0]), dt)
         ops.linear(x, self.w_in, proj, ws, batch.status)
+        tap = self.ctx.tap
+        if tap is not None:
+            tap("ssm_in", proj)
         conv = ws.get("ssm_conv", (n, cc), dt)
         self.conv.forward(proj[:, inner:inner + cc], batch, conv_cache, conv)
+        if tap is not None:
+            tap("ssm_conv", conv)
         y = ws.get("recurrence_out", (n, inner), torch.float32)
         ops.recurrence_ssd(conv, proj[:, inner + cc:], self.dt_bias, self.a_log, self.skip, state_cache.state, y, batch,
                            state_cache.slots, self.heads, self.groups, self.state, self.vdim)
-        tap = self.ctx.tap
         if tap is not None:
             tap("recurrence_out", y)
         gated = ws.get("recurrence_normed", (n, inner), dt)
         ops.group_rmsnorm(y, self.norm_w, self.eps, gated, self.norm_groups, gate=proj[:, :inner])
+        if tap is not None:
+            tap("recurrence_normed", gated)
         out = ws.get("mixer_out", (n, self.width), dt)
         ops.linear(gated, self.w_out, out, ws, batch.status)
         return out
@@ -120,16 +126,22 @@ class GatedLinearMixer(Mixer):
         n, hk, hv = x.shape[0], self.heads * self.dim, self.heads * self.vdim
         proj = ws.get("gla_in", (n, 2 * hk + hv), dt)
         ops.linear(x, self.w_qfv, proj, ws, batch.status)
+        tap = self.ctx.tap
+        if tap is not None:
+            tap("gla_in", proj)
         o = ws.get("gla_recurrence_out", (n, hv), torch.float32)
         ops.recurrence_gate(proj[:, :hk], proj[:, hk:2 * hk], proj[:, 2 * hk:], self.f_bias, self.lower, cache.state, o, batch,
                             cache.slots, self.heads, self.dim, self.vdim)
-        tap = self.ctx.tap
         if tap is not None:
             tap("gla_recurrence_out", o)
         normed = ws.get("gla_normed", (n, hv), dt)
         ops.group_rmsnorm(o, self.norm_w, self.eps, normed, self.heads)
+        if tap is not None:
+            tap("gla_normed", normed)
         out = ws.get(self.out_name, (n, self.width), dt)
         ops.linear(normed, self.w_out, out, ws, batch.status)
+        if tap is not None:
+            tap("gla_proj", out)
         return out
 
 
