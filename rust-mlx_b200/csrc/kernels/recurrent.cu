@@ -57,6 +57,67 @@ __global__ void short_conv_kernel(const T* __restrict__ x, int ld_x, const float
     if (write_state && keep > 0 && q_start[seq + 1] - 1 - t < keep) rows[(size_t)(pos % keep) * channels + c] = x[(size_t)t * ld_x + c];
 }
 
+// bfloat16, eight neighbouring channels a thread (16-byte accesses): channels, both row strides and every base address are
+// multiples of eight numbers.  The same sums in the same order as above.
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&v)[8]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+__global__ void short_conv8_kernel(const __nv_bfloat16* __restrict__ x, int ld_x, const float* __restrict__ w, const float* __restrict__ bias,
+                                   __nv_bfloat16* __restrict__ out, int ld_out, __nv_bfloat16* __restrict__ ring, int channels, int taps,
+                                   const int* __restrict__ positions, const int* __restrict__ seq_index, const int* __restrict__ slots,
+                                   const int* __restrict__ q_start, size_t total8, int act, int residual, int write_state) {
+    allow_dependents();
+    wait_for_prior_kernels();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total8) return;
+    const int c8 = channels >> 3;
+    const int t = (int)(idx / c8), c = (int)(idx - (size_t)t * c8) * 8;
+    const int seq = seq_index[t], pos = positions[t];
+    const int i = t - q_start[seq];
+    const int keep = taps - 1;
+    __nv_bfloat16* rows = ring + (size_t)slots[seq] * (keep > 0 ? keep : 1) * channels;
+    const uint4 cur_raw = *reinterpret_cast<const uint4*>(x + (size_t)t * ld_x + c);
+    float cur[8], acc[8];
+    unpack8(cur_raw, cur);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = bias ? bias[c + e] : 0.f;
+    for (int j = 0; j < taps; ++j) {
+        const int back = keep - j, p = pos - back;
+        float v[8];
+        if (back == 0) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = cur[e];
+        } else if (p < 0) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = 0.f;
+        } else if (back <= i) {
+            unpack8(*reinterpret_cast<const uint4*>(x + (size_t)(t - back) * ld_x + c), v);
+        } else {
+            unpack8(*reinterpret_cast<const uint4*>(rows + (size_t)(p % keep) * channels + c), v);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = fmaf(w[(size_t)(c + e) * taps + j], v[e], acc[e]);
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) {
+        float a = acc[e], b = acc[e + 1];
+        if (act == 1) { a = siluf_(a); b = siluf_(b); }
+        if (residual) { a += cur[e]; b += cur[e + 1]; }
+        __nv_bfloat162 r = __floats2bfloat162_rn(a, b);
+        o[e >> 1] = *reinterpret_cast<uint32_t*>(&r);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)t * ld_out + c) = make_uint4(o[0], o[1], o[2], o[3]);
+    if (write_state && keep > 0 && q_start[seq + 1] - 1 - t < keep)
+        *reinterpret_cast<uint4*>(rows + (size_t)(pos % keep) * channels + c) = cur_raw;
+}
+
 // The inputs of the last taps - 1 tokens of every sequence's portion go into the ring (after the kernel above has read it).
 template <typename T>
 __global__ void short_conv_state_kernel(const T* __restrict__ x, int ld_x, T* __restrict__ ring, int channels, int keep,
@@ -76,37 +137,102 @@ __global__ void short_conv_state_kernel(const T* __restrict__ x, int ld_x, T* __
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// The recurrence.  A warp owns 8 columns (v) of a head's state; the K rows of a column are shared by 4 lanes (lane =
-// part * 8 + column; a lane holds KPT consecutive rows), so loading and storing the state touches whole 32-byte sectors
-// and a token's output needs two shuffles.  A block has blockDim.x / 32 warps on neighbouring columns of one head of one
-// sequence; grid (column tiles, heads, sequences).  The step's a, k, q, v are formed in float by the whole block, STEPS
-// tokens at a time, into shared memory; the warps then run those tokens without meeting.
+// The recurrence, in two kernels.
+//
+// First the step's a, k, q (and for "ssd" the step sizes) are formed in float for all tokens at once, by as many threads
+// as there are numbers, into scratch rows laid out as the second kernel reads them: a head's K numbers in four runs of
+// KPT (one for each of the four lanes that share a column of the state), 4 floats of padding after each run, zeros
+// where K ends.  Then the scan: a warp owns 8 columns (v) of a head's state, the K rows of a column are shared by 4 lanes
+// (lane = part * 8 + column; a lane holds KPT consecutive rows), so loading and storing the state touches whole 32-byte
+// sectors and a token's output needs two shuffles.  A block has blockDim.x / 32 warps on neighbouring columns of one head
+// of one sequence; grid (column tiles, heads, sequences).  The rows of STEPS tokens at a time are copied into shared
+// memory (cp.async, two buffers: the next tokens' rows arrive while these are worked on), and the warps run those tokens
+// without meeting.  Every token is the same arithmetic in the same order wherever a step's portions are cut.
 constexpr int REC_COLS = 8, REC_PARTS = 4;
-enum { REC_SSD = 0, REC_GATE = 1 };
+__host__ __device__ constexpr int rec_row(int kpt) { return REC_PARTS * (kpt + 4); }
+__device__ __forceinline__ int rec_k_of(int j, int kpt) {   // which of the K numbers stands at place j of a row (-1: padding)
+    const int part = j / (kpt + 4), i = j - part * (kpt + 4);
+    return i < kpt ? part * kpt + i : -1;
+}
 
-struct RecurrenceArgs {
+// "ssd": conv rows [x (heads * V) | B (groups * K) | C (groups * K)], raw step sizes dt [tokens, heads].
+//   kf[t, g, :] = B, qf[t, g, :] = C (as floats, padded rows), step[t, h] = softplus(dt + bias), decay[t, h] = exp(-exp(A_log) step)
+template <typename T>
+__global__ void recurrence_prepare_ssd_kernel(const T* __restrict__ conv, int ld_conv, const T* __restrict__ dt, int ld_dt,
+                                              const float* __restrict__ dt_bias, const float* __restrict__ a_log, float* __restrict__ kf,
+                                              float* __restrict__ qf, float* __restrict__ step, float* __restrict__ decay, int heads,
+                                              int groups, int K, int V, int kpt, size_t total) {
+    allow_dependents();
+    wait_for_prior_kernels();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int row = rec_row(kpt), per_token = groups * row;
+    const int t = (int)(idx / per_token), r = (int)(idx - (size_t)t * per_token);
+    const int g = r / row, j = r - g * row;
+    const int k = rec_k_of(j, kpt);
+    const bool ok = k >= 0 && k < K;
+    const T* src = conv + (size_t)t * ld_conv + heads * V + g * K;
+    kf[idx] = ok ? to_float(src[k]) : 0.f;
+    qf[idx] = ok ? to_float(src[groups * K + k]) : 0.f;
+    for (int hh = r; hh < heads; hh += per_token) {     // (the token's threads share out its heads' scalars)
+        const float d = softplusf_(to_float(dt[(size_t)t * ld_dt + hh]) + dt_bias[hh]);
+        step[(size_t)t * heads + hh] = d;
+        decay[(size_t)t * heads + hh] = expf(-expf(a_log[hh]) * d);
+    }
+}
+
+// "gate": af = f = low + (1 - low) sigmoid(raw f + bias), kf = 1 - f, qf = silu(raw q), per head and channel, padded rows.
+template <typename T>
+__global__ void recurrence_prepare_gate_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ f, int ld_f,
+                                               const float* __restrict__ f_bias, const float* __restrict__ lower, float* __restrict__ af,
+                                               float* __restrict__ kf, float* __restrict__ qf, int heads, int K, int kpt, size_t total) {
+    allow_dependents();
+    wait_for_prior_kernels();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int row = rec_row(kpt), per_token = heads * row;
+    const int t = (int)(idx / per_token), r = (int)(idx - (size_t)t * per_token);
+    const int h = r / row, j = r - h * row;
+    const int k = rec_k_of(j, kpt);
+    float fv = 0.f, wv = 0.f, qv = 0.f;
+    if (k >= 0 && k < K) {
+        const float low = lower[h * K + k];
+        fv = low + (1.f - low) * sigmoidf_(to_float(f[(size_t)t * ld_f + h * K + k]) + f_bias[h * K + k]);
+        wv = 1.f - fv;
+        qv = siluf_(to_float(q[(size_t)t * ld_q + h * K + k]));
+    }
+    af[idx] = fv;
+    kf[idx] = wv;
+    qf[idx] = qv;
+}
+
+struct ScanArgs {
     float* state;           // [slots, heads, K, V]
     float* out;             // [tokens, heads * V]
     const int* q_start;
     const int* slots;
-    int heads, K, V, steps;
-    // ssd: conv = rows [x (heads * V) | B (groups * K) | C (groups * K)], dt = a column block of the input projection
-    // gate: q, f, v = column blocks of the projection
-    const void* a0; int ld0;    // ssd: conv rows            gate: q
-    const void* a1; int ld1;    // ssd: dt                   gate: f
-    const void* a2; int ld2;    // ssd: -                    gate: v
-    const float* p0;            // ssd: dt bias [heads]      gate: f bias [heads * K]
-    const float* p1;            // ssd: A_log [heads]        gate: lower bound [heads * K]
-    const float* p2;            // ssd: D [heads]
-    int groups;                 // ssd: groups of heads that share B and C
+    const float* af;        // a vector a head: [tokens, heads, row]; a scalar a head: [tokens, heads]
+    const float* kf;        // [tokens, row_heads, row]
+    const float* qf;
+    const void* v;          // [tokens, ld_v] of T, head h at columns h * V
+    const float* v_scale;   // [tokens, heads] or null: v is multiplied with it
+    const float* skip;      // [heads] or null: out += skip * (unscaled) v
+    int heads, row_heads, K, V, ld_v, steps;
 };
 
-template <typename T, int KPT, int MODE>
-__global__ void __launch_bounds__(256) linear_recurrence_kernel(const RecurrenceArgs A) {
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+template <typename T, int KPT, bool VEC>
+__global__ void __launch_bounds__(256) recurrence_scan_kernel(const ScanArgs A) {
     extern __shared__ __align__(16) float rec_smem[];
     allow_dependents();
     wait_for_prior_kernels();
-    constexpr int KROW = REC_PARTS * (KPT + 4);     // a lane's KPT numbers, 4 floats of padding between lanes' runs
+    constexpr int ROW = rec_row(KPT);
+    constexpr int MAXV = 4;                         // values of v a thread fetches for a buffer: steps * cols / threads = steps / 4
     const int warps = blockDim.x >> 5, cols = warps * REC_COLS;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int part = lane >> 3, col8 = lane & 7;
@@ -116,11 +242,11 @@ __global__ void __launch_bounds__(256) linear_recurrence_kernel(const Recurrence
     const bool v_ok = vcol < A.V;
     const int t0 = A.q_start[seq], t1 = A.q_start[seq + 1];
     const int K = A.K, V = A.V, H = A.heads, STEPS = A.steps;
-    float* qs = rec_smem;                        // [STEPS][KROW]
-    float* ks = qs + STEPS * KROW;               // [STEPS][KROW]
-    float* as = ks + STEPS * KROW;               // gate: [STEPS][KROW]; ssd: [STEPS]
-    float* vs = as + (MODE == REC_GATE ? STEPS * KROW : STEPS);   // [STEPS][cols]
+    const int hk = h / (H / A.row_heads);           // the row that this head reads of kf and qf
+    // one buffer: q rows, k rows, (a rows | a scalars), v (scaled), v (as it came)
+    const int buf_floats = STEPS * ROW * 2 + (VEC ? STEPS * ROW : STEPS) + 2 * STEPS * cols;
     float* sbase = A.state + ((size_t)A.slots[seq] * H + h) * K * V;
+    const T* vsrc = (const T*)A.v;
 
     float S[KPT];
 #pragma unroll
@@ -128,68 +254,70 @@ __global__ void __launch_bounds__(256) linear_recurrence_kernel(const Recurrence
         const int k = part * KPT + i;
         S[i] = (v_ok && k < K) ? sbase[(size_t)k * V + vcol] : 0.f;
     }
-    const float skip = (MODE == REC_SSD && A.p2) ? A.p2[h] : 0.f;
+    const float skip = A.skip ? A.skip[h] : 0.f;
+    const int n_chunks = (t1 - t0 + STEPS - 1) / STEPS;
+    float vreg[MAXV], sreg[MAXV], areg = 0.f;
 
-    for (int ts = t0; ts < t1; ts += STEPS) {
-        const int ns = min(STEPS, t1 - ts);
-        __syncthreads();
-        // ---- the block forms the tokens' a, k, q, v
-        if (MODE == REC_SSD) {
-            const T* conv = (const T*)A.a0;
-            const T* dtp = (const T*)A.a1;
-            const int g = h / (H / A.groups);
-            const int b_off = H * V + g * K, c_off = H * V + A.groups * K + g * K;
-            for (int e = threadIdx.x; e < ns * REC_PARTS * KPT; e += blockDim.x) {
-                const int s = e / (REC_PARTS * KPT), k = e - s * (REC_PARTS * KPT);
-                const int t = ts + s;
-                const float dt = softplusf_(to_float(dtp[(size_t)t * A.ld1 + h]) + A.p0[h]);
-                const int at = s * KROW + (k / KPT) * (KPT + 4) + k % KPT;
-                float kb = 0.f, qc = 0.f;
-                if (k < K) {
-                    kb = dt * to_float(conv[(size_t)t * A.ld0 + b_off + k]);
-                    qc = to_float(conv[(size_t)t * A.ld0 + c_off + k]);
-                }
-                ks[at] = kb;
-                qs[at] = qc;
-                if (k == 0) as[s] = expf(-expf(A.p1[h]) * dt);
-            }
-            for (int e = threadIdx.x; e < ns * cols; e += blockDim.x) {
-                const int s = e / cols, j = e - s * cols;
-                vs[s * cols + j] = (v0 + j < V) ? to_float(conv[(size_t)(ts + s) * A.ld0 + h * V + v0 + j]) : 0.f;
-            }
-        } else {
-            const T* qp = (const T*)A.a0;
-            const T* fp = (const T*)A.a1;
-            const T* vp = (const T*)A.a2;
-            for (int e = threadIdx.x; e < ns * REC_PARTS * KPT; e += blockDim.x) {
-                const int s = e / (REC_PARTS * KPT), k = e - s * (REC_PARTS * KPT);
-                const int t = ts + s;
-                const int at = s * KROW + (k / KPT) * (KPT + 4) + k % KPT;
-                float f = 0.f, q = 0.f, w = 0.f;
-                if (k < K) {
-                    const float low = A.p1[h * K + k];
-                    f = low + (1.f - low) * sigmoidf_(to_float(fp[(size_t)t * A.ld1 + h * K + k]) + A.p0[h * K + k]);
-                    w = 1.f - f;
-                    q = siluf_(to_float(qp[(size_t)t * A.ld0 + h * K + k]));
-                }
-                as[at] = f;
-                ks[at] = w;
-                qs[at] = q;
-            }
-            for (int e = threadIdx.x; e < ns * cols; e += blockDim.x) {
-                const int s = e / cols, j = e - s * cols;
-                vs[s * cols + j] = (v0 + j < V) ? to_float(vp[(size_t)(ts + s) * A.ld2 + h * V + v0 + j]) : 0.f;
+    // the copies of a chunk's rows into buffer b, and its v (and scalars) into registers
+    auto fetch = [&](int c) {
+        float* buf = rec_smem + (c & 1) * buf_floats;
+        const int ts = t0 + c * STEPS, ns = min(STEPS, t1 - ts);
+        const int pieces = ROW / 4;
+        for (int e = threadIdx.x; e < ns * pieces; e += blockDim.x) {
+            const int s = e / pieces, j = (e - s * pieces) * 4;
+            const size_t at = ((size_t)(ts + s) * A.row_heads + hk) * ROW + j;
+            cp_async16(buf + s * ROW + j, A.qf + at);
+            cp_async16(buf + STEPS * ROW + s * ROW + j, A.kf + at);
+            if (VEC) cp_async16(buf + 2 * STEPS * ROW + s * ROW + j, A.af + ((size_t)(ts + s) * H + h) * ROW + j);
+        }
+        cp_async_commit();
+#pragma unroll
+        for (int r = 0; r < MAXV; ++r) {
+            const int e = threadIdx.x + r * blockDim.x;
+            const int s = e / cols, j = e - s * cols;
+            vreg[r] = 0.f;
+            sreg[r] = 1.f;
+            if (s < ns && v0 + j < V) {
+                vreg[r] = to_float(vsrc[(size_t)(ts + s) * A.ld_v + h * V + v0 + j]);
+                if (A.v_scale) sreg[r] = A.v_scale[(size_t)(ts + s) * H + h];
             }
         }
+        if (!VEC && threadIdx.x < ns) areg = A.af[(size_t)(ts + threadIdx.x) * H + h];
+    };
+    // the registers of chunk c go into its buffer
+    auto settle = [&](int c) {
+        float* buf = rec_smem + (c & 1) * buf_floats;
+        float* vs = buf + STEPS * ROW * 2 + (VEC ? STEPS * ROW : STEPS);
+#pragma unroll
+        for (int r = 0; r < MAXV; ++r) {
+            const int e = threadIdx.x + r * blockDim.x;
+            if (e < STEPS * cols) {
+                vs[e] = vreg[r] * sreg[r];
+                vs[STEPS * cols + e] = vreg[r];
+            }
+        }
+        if (!VEC && threadIdx.x < STEPS) buf[2 * STEPS * ROW + threadIdx.x] = areg;
+    };
+
+    if (n_chunks > 0) {
+        fetch(0);
+        settle(0);
+    }
+    for (int c = 0; c < n_chunks; ++c) {
+        const bool more = c + 1 < n_chunks;
+        if (more) fetch(c + 1);          // the next chunk's rows are on their way while this one is worked on
+        if (more) cp_async_wait_group<1>(); else cp_async_wait_group<0>();
         __syncthreads();
-        // ---- each warp runs the tokens on its columns
+        const float* buf = rec_smem + (c & 1) * buf_floats;
+        const float* vs = buf + STEPS * ROW * 2 + (VEC ? STEPS * ROW : STEPS);
+        const int ts = t0 + c * STEPS, ns = min(STEPS, t1 - ts);
         for (int s = 0; s < ns; ++s) {
             const float v = vs[s * cols + warp * REC_COLS + col8];
-            const float* qrow = qs + s * KROW + part * (KPT + 4);
-            const float* krow = ks + s * KROW + part * (KPT + 4);
+            const float* qrow = buf + s * ROW + part * (KPT + 4);
+            const float* krow = buf + STEPS * ROW + s * ROW + part * (KPT + 4);
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            if (MODE == REC_SSD) {
-                const float a = as[s];
+            if (!VEC) {
+                const float a = buf[2 * STEPS * ROW + s];
 #pragma unroll
                 for (int i = 0; i < KPT; i += 4) {
                     const float4 k4 = *reinterpret_cast<const float4*>(krow + i);
@@ -200,7 +328,7 @@ __global__ void __launch_bounds__(256) linear_recurrence_kernel(const Recurrence
                     S[i + 3] = fmaf(a, S[i + 3], k4.w * v); acc[3] = fmaf(S[i + 3], q4.w, acc[3]);
                 }
             } else {
-                const float* arow = as + s * KROW + part * (KPT + 4);
+                const float* arow = buf + 2 * STEPS * ROW + s * ROW + part * (KPT + 4);
 #pragma unroll
                 for (int i = 0; i < KPT; i += 4) {
                     const float4 a4 = *reinterpret_cast<const float4*>(arow + i);
@@ -215,8 +343,11 @@ __global__ void __launch_bounds__(256) linear_recurrence_kernel(const Recurrence
             float o = (acc[0] + acc[1]) + (acc[2] + acc[3]);
             o += __shfl_xor_sync(0xffffffffu, o, 8);
             o += __shfl_xor_sync(0xffffffffu, o, 16);
-            if (part == 0 && v_ok) A.out[((size_t)(ts + s) * H + h) * V + vcol] = fmaf(skip, v, o);
+            if (part == 0 && v_ok)
+                A.out[((size_t)(ts + s) * H + h) * V + vcol] = fmaf(skip, vs[STEPS * cols + s * cols + warp * REC_COLS + col8], o);
         }
+        if (more) settle(c + 1);          // (the other buffer: nobody reads it before the next barrier)
+        __syncthreads();
     }
 #pragma unroll
     for (int i = 0; i < KPT; ++i) {
@@ -269,28 +400,25 @@ __global__ void sigmoid_gate_kernel(const T* o, int o_head, const T* __restrict_
     out[idx] = from_float<T>(v * sigmoidf_(to_float(gate[t * ld_gate + r])));
 }
 
-template <typename T, int MODE>
-int launch_recurrence(const RecurrenceArgs& a, int n_seqs, int warps, cudaStream_t s) {
+static int rec_kpt(int K) { return K <= 32 ? 8 : (K <= 64 ? 16 : (K <= 128 ? 32 : 64)); }
+static int rec_steps(int kpt) { return kpt <= 16 ? 16 : (kpt == 32 ? 8 : 4); }
+
+template <typename T, bool VEC>
+int launch_scan(const ScanArgs& a, int n_seqs, int warps, cudaStream_t s) {
     const int cols = warps * REC_COLS;
     dim3 grid((a.V + cols - 1) / cols, a.heads, n_seqs), block(warps * 32);
-    RecurrenceArgs args = a;
-    auto smem_of = [&](int kpt, int steps) {
-        const int krow = REC_PARTS * (kpt + 4);
-        return (size_t)(steps * krow * 2 + (MODE == REC_GATE ? steps * krow : steps) + steps * cols) * sizeof(float);
-    };
-#define RMX_REC_CASE(KPT, STEPS)                                                                                           \
-    do {                                                                                                                   \
-        args.steps = STEPS;                                                                                                \
-        RMX_CHECK_LAUNCHED(launch_dependent(linear_recurrence_kernel<T, KPT, MODE>, grid, block, smem_of(KPT, STEPS), s, args), \
-                           "linear_recurrence");                                                                           \
-        return 0;                                                                                                          \
-    } while (0)
-    if (a.K <= 32) RMX_REC_CASE(8, 16);
-    if (a.K <= 64) RMX_REC_CASE(16, 16);
-    if (a.K <= 128) RMX_REC_CASE(32, 8);
-    if (a.K <= 256) RMX_REC_CASE(64, 4);
-#undef RMX_REC_CASE
-    RMX_FAIL("linear_recurrence: a state of %d rows a head is beyond 256", a.K);
+    ScanArgs args = a;
+    const int kpt = rec_kpt(a.K);
+    args.steps = rec_steps(kpt);
+    const int row = rec_row(kpt);
+    const size_t smem = 2 * (size_t)(args.steps * row * 2 + (VEC ? args.steps * row : args.steps) + 2 * args.steps * cols) * sizeof(float);
+    switch (kpt) {
+        case 8: RMX_CHECK_LAUNCHED(launch_dependent(recurrence_scan_kernel<T, 8, VEC>, grid, block, smem, s, args), "recurrence_scan"); break;
+        case 16: RMX_CHECK_LAUNCHED(launch_dependent(recurrence_scan_kernel<T, 16, VEC>, grid, block, smem, s, args), "recurrence_scan"); break;
+        case 32: RMX_CHECK_LAUNCHED(launch_dependent(recurrence_scan_kernel<T, 32, VEC>, grid, block, smem, s, args), "recurrence_scan"); break;
+        default: RMX_CHECK_LAUNCHED(launch_dependent(recurrence_scan_kernel<T, 64, VEC>, grid, block, smem, s, args), "recurrence_scan"); break;
+    }
+    return 0;
 }
 }  // namespace
 
@@ -316,6 +444,11 @@ RMX_API int rmx_short_conv(const void* x, int ld_x, const float* w, const float*
                                                 0, s, (const float*)x, ld_x, (float*)ring, channels, keep, positions, slots, q_start, n_seqs),
                                "short_conv_state");
     } else if (dtype == RMX_BF16) {
+        if (channels % 8 == 0 && ld_x % 8 == 0 && ld_out % 8 == 0 && (((uintptr_t)x | (uintptr_t)out | (uintptr_t)ring) & 15) == 0)
+            RMX_CHECK_LAUNCHED(launch_dependent(short_conv8_kernel, dim3((unsigned)((total / 8 + threads - 1) / threads)), dim3(threads), 0, s,
+                                                (const __nv_bfloat16*)x, ld_x, w, bias, (__nv_bfloat16*)out, ld_out, (__nv_bfloat16*)ring, channels,
+                                                taps, positions, seq_index, slots, q_start, total / 8, act, residual, single_tokens), "short_conv");
+        else
         RMX_CHECK_LAUNCHED(launch_dependent(short_conv_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, s, (const __nv_bfloat16*)x, ld_x, w,
                                             bias, (__nv_bfloat16*)out, ld_out, (__nv_bfloat16*)ring, channels, taps, positions, seq_index, slots,
                                             q_start, total, act, residual, single_tokens), "short_conv");
@@ -329,33 +462,53 @@ RMX_API int rmx_short_conv(const void* x, int ld_x, const float* w, const float*
     return 0;
 }
 
-// mode 0 ("ssd"): a0 = conv rows [x | B | C], a1 = dt columns, p0 = dt bias, p1 = A_log, p2 = D (or null), groups.
-// mode 1 ("gate"): a0 = q, a1 = f, a2 = v columns, p0 = f bias, p1 = lower bound.
-RMX_API int rmx_linear_recurrence(int mode, float* state, float* out, const int* q_start, const int* slots, int n_seqs, int heads, int K,
-                                  int V, const void* a0, int ld0, const void* a1, int ld1, const void* a2, int ld2, const float* p0,
-                                  const float* p1, const float* p2, int groups, int warps, int dtype, void* stream) {
-    if (n_seqs == 0) return 0;
-    RMX_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && heads > 0 && heads <= 65535 && K > 0 && V > 0, "linear_recurrence: bad sizes");
-    RMX_REQUIRE(state && out && q_start && slots && a0 && a1 && p0 && p1, "linear_recurrence: a null pointer");
+// How many floats of scratch the recurrence wants for n_tokens tokens: (floats of each padded array, padded row length).
+RMX_API long long rmx_recurrence_row(int K) { return K > 0 && K <= 256 ? rec_row(rec_kpt(K)) : -1; }
+
+// mode 0 ("ssd"): a0 = conv rows [x | B | C], a1 = dt columns, p0 = dt bias, p1 = A_log, p2 = D (or null), groups;
+//   scratch: kf, qf [tokens, groups, row] and s0 = step, s1 = decay [tokens, heads].
+// mode 1 ("gate"): a0 = q, a1 = f, a2 = v columns, p0 = f bias, p1 = lower bound; scratch: s0 = af, kf, qf [tokens, heads, row].
+RMX_API int rmx_linear_recurrence(int mode, float* state, float* out, const int* q_start, const int* slots, int n_seqs, int n_tokens,
+                                  int heads, int K, int V, const void* a0, int ld0, const void* a1, int ld1, const void* a2, int ld2,
+                                  const float* p0, const float* p1, const float* p2, int groups, float* kf, float* qf, float* s0, float* s1,
+                                  int warps, int dtype, void* stream) {
+    if (n_seqs == 0 || n_tokens == 0) return 0;
+    RMX_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && heads > 0 && heads <= 65535 && K > 0 && V > 0 && n_tokens > 0, "linear_recurrence: bad sizes");
+    RMX_REQUIRE(K <= 256, "linear_recurrence: a state of %d rows a head is beyond 256", K);
+    RMX_REQUIRE(state && out && q_start && slots && a0 && a1 && p0 && p1 && kf && qf && s0, "linear_recurrence: a null pointer");
     RMX_REQUIRE(warps >= 1 && warps <= 8, "linear_recurrence: 1 to 8 warps a block");
-    RecurrenceArgs a;
-    a.state = state; a.out = out; a.q_start = q_start; a.slots = slots;
-    a.heads = heads; a.K = K; a.V = V; a.steps = 0;
-    a.a0 = a0; a.ld0 = ld0; a.a1 = a1; a.ld1 = ld1; a.a2 = a2; a.ld2 = ld2;
-    a.p0 = p0; a.p1 = p1; a.p2 = p2; a.groups = groups;
+    RMX_REQUIRE(dtype == RMX_F32 || dtype == RMX_BF16, "linear_recurrence: unknown dtype %d", dtype);
+    const int kpt = rec_kpt(K), row = rec_row(kpt), threads = 256;
     cudaStream_t s = (cudaStream_t)stream;
-    if (mode == REC_SSD) {
-        RMX_REQUIRE(groups > 0 && heads % groups == 0, "linear_recurrence: %d heads in %d groups", heads, groups);
-        if (dtype == RMX_F32) return launch_recurrence<float, REC_SSD>(a, n_seqs, warps, s);
-        if (dtype == RMX_BF16) return launch_recurrence<__nv_bfloat16, REC_SSD>(a, n_seqs, warps, s);
-    } else if (mode == REC_GATE) {
-        RMX_REQUIRE(a2 != nullptr, "linear_recurrence: the gated form needs values");
-        if (dtype == RMX_F32) return launch_recurrence<float, REC_GATE>(a, n_seqs, warps, s);
-        if (dtype == RMX_BF16) return launch_recurrence<__nv_bfloat16, REC_GATE>(a, n_seqs, warps, s);
-    } else {
-        RMX_FAIL("linear_recurrence: unknown mode %d", mode);
+    ScanArgs a;
+    a.state = state; a.out = out; a.q_start = q_start; a.slots = slots; a.kf = kf; a.qf = qf;
+    a.heads = heads; a.K = K; a.V = V; a.steps = 0;
+    if (mode == 0) {
+        RMX_REQUIRE(groups > 0 && heads % groups == 0 && s1, "linear_recurrence: %d heads in %d groups", heads, groups);
+        const size_t total = (size_t)n_tokens * groups * row;
+        const dim3 grid((unsigned)((total + threads - 1) / threads));
+        if (dtype == RMX_F32)
+            RMX_CHECK_LAUNCHED(launch_dependent(recurrence_prepare_ssd_kernel<float>, grid, dim3(threads), 0, s, (const float*)a0, ld0, (const float*)a1,
+                                                ld1, p0, p1, kf, qf, s0, s1, heads, groups, K, V, kpt, total), "recurrence_prepare");
+        else
+            RMX_CHECK_LAUNCHED(launch_dependent(recurrence_prepare_ssd_kernel<__nv_bfloat16>, grid, dim3(threads), 0, s, (const __nv_bfloat16*)a0, ld0,
+                                                (const __nv_bfloat16*)a1, ld1, p0, p1, kf, qf, s0, s1, heads, groups, K, V, kpt, total),
+                               "recurrence_prepare");
+        a.af = s1; a.v = a0; a.ld_v = ld0; a.v_scale = s0; a.skip = p2; a.row_heads = groups;
+        return dtype == RMX_F32 ? launch_scan<float, false>(a, n_seqs, warps, s) : launch_scan<__nv_bfloat16, false>(a, n_seqs, warps, s);
     }
-    RMX_FAIL("linear_recurrence: unknown dtype %d", dtype);
+    RMX_REQUIRE(mode == 1, "linear_recurrence: unknown mode %d", mode);
+    RMX_REQUIRE(a2 != nullptr, "linear_recurrence: the gated form needs values");
+    const size_t total = (size_t)n_tokens * heads * row;
+    const dim3 grid((unsigned)((total + threads - 1) / threads));
+    if (dtype == RMX_F32)
+        RMX_CHECK_LAUNCHED(launch_dependent(recurrence_prepare_gate_kernel<float>, grid, dim3(threads), 0, s, (const float*)a0, ld0, (const float*)a1,
+                                            ld1, p0, p1, s0, kf, qf, heads, K, kpt, total), "recurrence_prepare");
+    else
+        RMX_CHECK_LAUNCHED(launch_dependent(recurrence_prepare_gate_kernel<__nv_bfloat16>, grid, dim3(threads), 0, s, (const __nv_bfloat16*)a0, ld0,
+                                            (const __nv_bfloat16*)a1, ld1, p0, p1, s0, kf, qf, heads, K, kpt, total), "recurrence_prepare");
+    a.af = s0; a.v = a2; a.ld_v = ld2; a.v_scale = nullptr; a.skip = nullptr; a.row_heads = heads;
+    return dtype == RMX_F32 ? launch_scan<float, true>(a, n_seqs, warps, s) : launch_scan<__nv_bfloat16, true>(a, n_seqs, warps, s);
 }
 
 RMX_API int rmx_group_rmsnorm(const float* y, const void* gate, int ld_gate, const float* w, int period, float eps, void* out, int ld_out,

@@ -397,7 +397,21 @@ def _cols(t, name):
     return c_void_p(t.data_ptr()), c_int(t.stride(0))
 
 
-def recurrence_ssd(conv, dt, dt_bias, a_log, d_skip, state, out, batch, slots, heads, groups, k, v):
+def _recurrence_scratch(workspace, n, row_heads, heads, k, vector_decay):
+    """Float scratch of the recurrence's two kernels: rows of k and q padded as the scan reads them, and either the decays'
+    rows (a vector a head) or two scalars a token and head."""
+    ws = workspace if workspace is not None else _own_workspace()
+    row = kernels_library().rmx_recurrence_row(c_int(k))
+    if row < 0:
+        raise KernelError(f"recurrence: a state of {k} rows a head is beyond 256")
+    kf = ws.get("recurrence_k", (n, row_heads, row), torch.float32)
+    qf = ws.get("recurrence_q", (n, row_heads, row), torch.float32)
+    if vector_decay:
+        return kf, qf, ws.get("recurrence_a", (n, heads, row), torch.float32), None
+    return kf, qf, ws.get("recurrence_step", (n, heads), torch.float32), ws.get("recurrence_decay", (n, heads), torch.float32)
+
+
+def recurrence_ssd(conv, dt, dt_bias, a_log, d_skip, state, out, batch, slots, heads, groups, k, v, workspace=None):
     """Per head S_t = exp(-exp(A_log) dt_t) S_(t-1) + dt_t B_t x_t^T, y_t = S_t^T C_t + D x_t, dt = softplus(raw + bias):
     ``conv`` rows [x (heads * v) | B (groups * k) | C (groups * k)], ``dt`` [tokens, heads] raw, ``state`` float32
     [slots, heads, k, v] (read and written), ``out`` float32 [tokens, heads * v]."""
@@ -406,18 +420,19 @@ def recurrence_ssd(conv, dt, dt_bias, a_log, d_skip, state, out, batch, slots, h
     if conv.shape[1] != heads * v + 2 * groups * k or dt.shape != (n, heads) or out.shape != (n, heads * v) or state.shape[1:] != (heads, k, v) \
             or dt.dtype != conv.dtype:
         raise KernelError("recurrence_ssd: shapes do not fit")
+    kf, qf, s0, s1 = _recurrence_scratch(workspace, n, groups, heads, k, False)
     p0, l0 = _cols(conv, "conv")
     p1, l1 = _cols(dt, "dt")
     check(lib.rmx_linear_recurrence(c_int(0), _ptr(state, torch.float32, "state"), _ptr(out, torch.float32, "out"),
                                     _ptr(batch.q_start, torch.int32, "q_start"), _ptr(slots, torch.int32, "slots"), c_int(batch.n_seqs),
-                                    c_int(heads), c_int(k), c_int(v), p0, l0, p1, l1, c_void_p(0), c_int(0),
+                                    c_int(n), c_int(heads), c_int(k), c_int(v), p0, l0, p1, l1, c_void_p(0), c_int(0),
                                     _ptr(dt_bias, torch.float32, "dt_bias"), _ptr(a_log, torch.float32, "A_log"),
-                                    _ptr(d_skip, torch.float32, "D"), c_int(groups), c_int(_recurrence_warps(batch, heads, v)),
-                                    c_int(dtype_code(conv)), _stream()))
-    _launched()
+                                    _ptr(d_skip, torch.float32, "D"), c_int(groups), _ptr(kf), _ptr(qf), _ptr(s0), _ptr(s1),
+                                    c_int(_recurrence_warps(batch, heads, v)), c_int(dtype_code(conv)), _stream()))
+    _launched(2)
 
 
-def recurrence_gate(q, f, v, f_bias, lower, state, out, batch, slots, heads, k, vdim):
+def recurrence_gate(q, f, v, f_bias, lower, state, out, batch, slots, heads, k, vdim, workspace=None):
     """Per head S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T silu(q_t), f = lower + (1 - lower) sigmoid(raw + bias):
     ``q`` and ``f`` [tokens, heads * k] raw projections, ``v`` [tokens, heads * vdim] (columns of wider rows allowed),
     ``state`` float32 [slots, heads, k, vdim], ``out`` float32 [tokens, heads * vdim]."""
@@ -426,15 +441,17 @@ def recurrence_gate(q, f, v, f_bias, lower, state, out, batch, slots, heads, k, 
     if q.shape != (n, heads * k) or f.shape != (n, heads * k) or v.shape != (n, heads * vdim) or out.shape != (n, heads * vdim) \
             or state.shape[1:] != (heads, k, vdim) or f.dtype != q.dtype or v.dtype != q.dtype:
         raise KernelError("recurrence_gate: shapes do not fit")
+    kf, qf, s0, _ = _recurrence_scratch(workspace, n, heads, heads, k, True)
     p0, l0 = _cols(q, "q")
     p1, l1 = _cols(f, "f")
     p2, l2 = _cols(v, "v")
     check(lib.rmx_linear_recurrence(c_int(1), _ptr(state, torch.float32, "state"), _ptr(out, torch.float32, "out"),
                                     _ptr(batch.q_start, torch.int32, "q_start"), _ptr(slots, torch.int32, "slots"), c_int(batch.n_seqs),
-                                    c_int(heads), c_int(k), c_int(vdim), p0, l0, p1, l1, p2, l2,
+                                    c_int(n), c_int(heads), c_int(k), c_int(vdim), p0, l0, p1, l1, p2, l2,
                                     _ptr(f_bias, torch.float32, "f_bias"), _ptr(lower, torch.float32, "lower"), c_void_p(0), c_int(1),
+                                    _ptr(kf), _ptr(qf), _ptr(s0), c_void_p(0),
                                     c_int(_recurrence_warps(batch, heads, vdim)), c_int(dtype_code(q)), _stream()))
-    _launched()
+    _launched(2)
 
 
 def group_rmsnorm(y, weight, eps, out, groups, gate=None, out_scale=1.0):

@@ -78,7 +78,7 @@ class StateSpaceMixer(Mixer):
             tap("ssm_conv", conv)
         y = ws.get("recurrence_out", (n, inner), torch.float32)
         ops.recurrence_ssd(conv, proj[:, inner + cc:], self.dt_bias, self.a_log, self.skip, state_cache.state, y, batch,
-                           state_cache.slots, self.heads, self.groups, self.state, self.vdim)
+                           state_cache.slots, self.heads, self.groups, self.state, self.vdim, workspace=ws)
         if tap is not None:
             tap("recurrence_out", y)
         gated = ws.get("recurrence_normed", (n, inner), dt)
@@ -131,7 +131,7 @@ class GatedLinearMixer(Mixer):
             tap("gla_in", proj)
         o = ws.get("gla_recurrence_out", (n, hv), torch.float32)
         ops.recurrence_gate(proj[:, :hk], proj[:, hk:2 * hk], proj[:, 2 * hk:], self.f_bias, self.lower, cache.state, o, batch,
-                            cache.slots, self.heads, self.dim, self.vdim)
+                            cache.slots, self.heads, self.dim, self.vdim, workspace=ws)
         if tap is not None:
             tap("gla_recurrence_out", o)
         normed = ws.get("gla_normed", (n, hv), dt)

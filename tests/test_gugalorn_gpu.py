@@ -76,10 +76,12 @@ def test_short_convolution_in_portions_through_its_ring(dtype, taps, channels, a
     got = [torch.zeros(n, channels, dtype=dt) for n in lengths]
     for batch, rows in Steps(cuts):
         xin = torch.cat([x[s][a:a + n] for s, a, n in rows]).to(DEV)
-        wide = torch.full((xin.shape[0], channels + 5), float("nan"), dtype=dt, device=DEV)    # columns of wider rows
-        wide[:, 2:2 + channels] = xin
+        # columns of wider rows: at a place that the kernel of eight channels a thread takes (bfloat16), or not
+        lead, extra = (8, 16) if channels % 8 == 0 and taps != 2 else (2, 5)
+        wide = torch.full((xin.shape[0], channels + extra), float("nan"), dtype=dt, device=DEV)
+        wide[:, lead:lead + channels] = xin
         out = torch.empty_like(xin)
-        ops().short_conv(wide[:, 2:2 + channels], w.to(DEV), b.to(DEV) if bias else None, out, ring, batch,
+        ops().short_conv(wide[:, lead:lead + channels], w.to(DEV), b.to(DEV) if bias else None, out, ring, batch,
                          slots[[s for s, _, _ in rows]].contiguous(), act, residual)
         at = 0
         for s, a, n in rows:
