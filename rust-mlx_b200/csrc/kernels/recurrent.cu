@@ -1,5 +1,5 @@
 // Layers that carry a state of fixed size from token to token: a short causal convolution over time, and the
-// gated linear recurrence  S_t = diag(a_t) S_(t-1) + k_t v_t^T,  o_t = S_t^T q_t  (S is K x V per head, float).
+// gated linear recurrence  S_t = diag(a_t) S_(t-1) + k_t v_t^T,  o_t = S_t^T q_t  (S is K x V per head, float, kept transposed).
 //
 // Two ways of forming a_t, k_t, q_t, v_t from a layer's projections are built:
 //   "ssd"  (a state-space layer with a scalar decay a head): a = exp(-exp(A_log) dt), dt = softplus(raw + bias),
@@ -18,7 +18,8 @@ __device__ __forceinline__ float siluf_(float x) { return x / (1.f + expf(-x)); 
 __device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// Causal convolution over time on each channel:  y_t = act(bias + sum_j w[c, j] x_(t - taps + 1 + j)) (+ x_t).
+// Causal convolution over time on each channel:  y_t = act(bias + sum_j w[j, c] x_(t - taps + 1 + j)) (+ x_t); the weight
+// is held taps-major ([taps, channels]: neighbouring threads read neighbouring numbers).
 // The last taps - 1 inputs of every sequence live in `ring` [slots, taps - 1, channels], input p at row p % (taps - 1).
 // Inputs of the step's own tokens come from `x`, older ones from the ring, positions below 0 are zero.
 // write_state: a thread whose token is among the last taps - 1 of its sequence's portion stores its input.  That is
@@ -49,7 +50,7 @@ __global__ void short_conv_kernel(const T* __restrict__ x, int ld_x, const float
         else if (p < 0) v = 0.f;
         else if (back <= i) v = to_float(x[(size_t)(t - back) * ld_x + c]);
         else v = to_float(rows[(size_t)(p % keep) * channels + c]);
-        acc = fmaf(w[(size_t)c * taps + j], v, acc);
+        acc = fmaf(w[(size_t)j * channels + c], v, acc);
     }
     if (act == 1) acc = siluf_(acc);
     if (residual) acc += cur;
@@ -101,8 +102,11 @@ __global__ void short_conv8_kernel(const __nv_bfloat16* __restrict__ x, int ld_x
         } else {
             unpack8(*reinterpret_cast<const uint4*>(rows + (size_t)(p % keep) * channels + c), v);
         }
+        const float4 w0 = *reinterpret_cast<const float4*>(w + (size_t)j * channels + c);
+        const float4 w1 = *reinterpret_cast<const float4*>(w + (size_t)j * channels + c + 4);
+        const float wj[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = fmaf(w[(size_t)(c + e) * taps + j], v[e], acc[e]);
+        for (int e = 0; e < 8; ++e) acc[e] = fmaf(wj[e], v[e], acc[e]);
     }
     uint32_t o[4];
 #pragma unroll
@@ -140,18 +144,21 @@ __global__ void short_conv_state_kernel(const T* __restrict__ x, int ld_x, T* __
 // The recurrence, in two kernels.
 //
 // First the step's a, k, q (and for "ssd" the step sizes) are formed in float for all tokens at once, by as many threads
-// as there are numbers, into scratch rows laid out as the second kernel reads them: a head's K numbers in four runs of
-// KPT (one for each of the four lanes that share a column of the state), 4 floats of padding after each run, zeros
-// where K ends.  Then the scan: a warp owns 8 columns (v) of a head's state, the K rows of a column are shared by 4 lanes
-// (lane = part * 8 + column; a lane holds KPT consecutive rows), so loading and storing the state touches whole 32-byte
-// sectors and a token's output needs two shuffles.  A block has blockDim.x / 32 warps on neighbouring columns of one head
+// as there are numbers, into scratch rows laid out as the second kernel reads them: a head's K numbers in eight runs of
+// KPT (one for each of the eight lanes that share a column of the state), some floats of padding after each run, zeros
+// where K ends.  Then the scan: a warp owns 8 columns (v) of a head's state, the K numbers of a column are shared by 8
+// lanes and a lane holds KPT consecutive ones of TWO neighbouring columns (what it reads of a, k, q from shared memory
+// serves both: the loop is bound by those reads), the state is kept [V, K] so that a lane's numbers are neighbours in
+// memory, and a token's outputs need three shuffles each.  A block has blockDim.x / 32 warps on neighbouring columns of one head
 // of one sequence; grid (column tiles, heads, sequences).  The rows of STEPS tokens at a time are copied into shared
 // memory (cp.async, two buffers: the next tokens' rows arrive while these are worked on), and the warps run those tokens
 // without meeting.  Every token is the same arithmetic in the same order wherever a step's portions are cut.
-constexpr int REC_COLS = 8, REC_PARTS = 4;
-__host__ __device__ constexpr int rec_row(int kpt) { return REC_PARTS * (kpt + 4); }
+constexpr int REC_COLS = 8, REC_PARTS = 8;   // a warp's columns (two a lane), lanes that share a column
+__host__ __device__ constexpr int rec_pad(int kpt) { return kpt == 4 ? 0 : 4; }   // (keeps the lanes' 16-byte reads on different banks)
+__host__ __device__ constexpr int rec_row(int kpt) { return REC_PARTS * (kpt + rec_pad(kpt)); }
 __device__ __forceinline__ int rec_k_of(int j, int kpt) {   // which of the K numbers stands at place j of a row (-1: padding)
-    const int part = j / (kpt + 4), i = j - part * (kpt + 4);
+    const int run = kpt + rec_pad(kpt);
+    const int part = j / run, i = j - part * run;
     return i < kpt ? part * kpt + i : -1;
 }
 
@@ -161,13 +168,13 @@ template <typename T>
 __global__ void recurrence_prepare_ssd_kernel(const T* __restrict__ conv, int ld_conv, const T* __restrict__ dt, int ld_dt,
                                               const float* __restrict__ dt_bias, const float* __restrict__ a_log, float* __restrict__ kf,
                                               float* __restrict__ qf, float* __restrict__ step, float* __restrict__ decay, int heads,
-                                              int groups, int K, int V, int kpt, size_t total) {
+                                              int groups, int K, int V, int kpt) {
     allow_dependents();
     wait_for_prior_kernels();
-    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= total) return;
     const int row = rec_row(kpt), per_token = groups * row;
-    const int t = (int)(idx / per_token), r = (int)(idx - (size_t)t * per_token);
+    const int t = blockIdx.x, r = blockIdx.y * blockDim.x + threadIdx.x;     // grid (tokens, pieces of a token's rows)
+    if (r >= per_token) return;
+    const size_t idx = (size_t)t * per_token + r;
     const int g = r / row, j = r - g * row;
     const int k = rec_k_of(j, kpt);
     const bool ok = k >= 0 && k < K;
@@ -185,13 +192,13 @@ __global__ void recurrence_prepare_ssd_kernel(const T* __restrict__ conv, int ld
 template <typename T>
 __global__ void recurrence_prepare_gate_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ f, int ld_f,
                                                const float* __restrict__ f_bias, const float* __restrict__ lower, float* __restrict__ af,
-                                               float* __restrict__ kf, float* __restrict__ qf, int heads, int K, int kpt, size_t total) {
+                                               float* __restrict__ kf, float* __restrict__ qf, int heads, int K, int kpt) {
     allow_dependents();
     wait_for_prior_kernels();
-    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= total) return;
     const int row = rec_row(kpt), per_token = heads * row;
-    const int t = (int)(idx / per_token), r = (int)(idx - (size_t)t * per_token);
+    const int t = blockIdx.x, r = blockIdx.y * blockDim.x + threadIdx.x;     // grid (tokens, pieces of a token's rows)
+    if (r >= per_token) return;
+    const size_t idx = (size_t)t * per_token + r;
     const int h = r / row, j = r - h * row;
     const int k = rec_k_of(j, kpt);
     float fv = 0.f, wv = 0.f, qv = 0.f;
@@ -207,7 +214,7 @@ __global__ void recurrence_prepare_gate_kernel(const T* __restrict__ q, int ld_q
 }
 
 struct ScanArgs {
-    float* state;           // [slots, heads, K, V]
+    float* state;           // [slots, heads, V, K]
     float* out;             // [tokens, heads * V]
     const int* q_start;
     const int* slots;
@@ -224,6 +231,7 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+__device__ __forceinline__ void st_global(float* p, float v) { asm volatile("st.global.f32 [%0], %1;\n" ::"l"(p), "f"(v)); }
 template <int N> __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
 template <typename T, int KPT, bool VEC>
@@ -231,15 +239,15 @@ __global__ void __launch_bounds__(256) recurrence_scan_kernel(const ScanArgs A) 
     extern __shared__ __align__(16) float rec_smem[];
     allow_dependents();
     wait_for_prior_kernels();
-    constexpr int ROW = rec_row(KPT);
+    constexpr int ROW = rec_row(KPT), RUN = KPT + rec_pad(KPT);
     constexpr int MAXV = 4;                         // values of v a thread fetches for a buffer: steps * cols / threads = steps / 4
     const int warps = blockDim.x >> 5, cols = warps * REC_COLS;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int part = lane >> 3, col8 = lane & 7;
+    const int part = lane & 7, pair = lane >> 3;    // the lane's two columns are 2 * pair and 2 * pair + 1 of the warp's eight
     const int h = blockIdx.y, seq = blockIdx.z;
     const int v0 = blockIdx.x * cols;
-    const int vcol = v0 + warp * REC_COLS + col8;
-    const bool v_ok = vcol < A.V;
+    const int vcol = v0 + warp * REC_COLS + 2 * pair;
+    const bool v_ok = vcol < A.V, v_ok1 = vcol + 1 < A.V;
     const int t0 = A.q_start[seq], t1 = A.q_start[seq + 1];
     const int K = A.K, V = A.V, H = A.heads, STEPS = A.steps;
     const int hk = h / (H / A.row_heads);           // the row that this head reads of kf and qf
@@ -248,15 +256,17 @@ __global__ void __launch_bounds__(256) recurrence_scan_kernel(const ScanArgs A) 
     float* sbase = A.state + ((size_t)A.slots[seq] * H + h) * K * V;
     const T* vsrc = (const T*)A.v;
 
-    float S[KPT];
+    float S[KPT], S1[KPT];
 #pragma unroll
     for (int i = 0; i < KPT; ++i) {
         const int k = part * KPT + i;
-        S[i] = (v_ok && k < K) ? sbase[(size_t)k * V + vcol] : 0.f;
+        S[i] = (v_ok && k < K) ? sbase[(size_t)vcol * K + k] : 0.f;
+        S1[i] = (v_ok1 && k < K) ? sbase[(size_t)(vcol + 1) * K + k] : 0.f;
     }
     const float skip = A.skip ? A.skip[h] : 0.f;
     const int n_chunks = (t1 - t0 + STEPS - 1) / STEPS;
-    float vreg[MAXV], sreg[MAXV], areg = 0.f;
+    T vreg[MAXV];
+    float sreg[MAXV], areg = 0.f;
 
     // the copies of a chunk's rows into buffer b, and its v (and scalars) into registers
     auto fetch = [&](int c) {
@@ -275,10 +285,10 @@ __global__ void __launch_bounds__(256) recurrence_scan_kernel(const ScanArgs A) 
         for (int r = 0; r < MAXV; ++r) {
             const int e = threadIdx.x + r * blockDim.x;
             const int s = e / cols, j = e - s * cols;
-            vreg[r] = 0.f;
+            vreg[r] = from_float<T>(0.f);
             sreg[r] = 1.f;
-            if (s < ns && v0 + j < V) {
-                vreg[r] = to_float(vsrc[(size_t)(ts + s) * A.ld_v + h * V + v0 + j]);
+            if (s < ns && v0 + j < V) {      // (kept as they come: a conversion here would wait for the load)
+                vreg[r] = vsrc[(size_t)(ts + s) * A.ld_v + h * V + v0 + j];
                 if (A.v_scale) sreg[r] = A.v_scale[(size_t)(ts + s) * H + h];
             }
         }
@@ -292,8 +302,8 @@ __global__ void __launch_bounds__(256) recurrence_scan_kernel(const ScanArgs A) 
         for (int r = 0; r < MAXV; ++r) {
             const int e = threadIdx.x + r * blockDim.x;
             if (e < STEPS * cols) {
-                vs[e] = vreg[r] * sreg[r];
-                vs[STEPS * cols + e] = vreg[r];
+                vs[e] = to_float(vreg[r]) * sreg[r];
+                vs[STEPS * cols + e] = to_float(vreg[r]);
             }
         }
         if (!VEC && threadIdx.x < STEPS) buf[2 * STEPS * ROW + threadIdx.x] = areg;
@@ -311,40 +321,38 @@ __global__ void __launch_bounds__(256) recurrence_scan_kernel(const ScanArgs A) 
         const float* buf = rec_smem + (c & 1) * buf_floats;
         const float* vs = buf + STEPS * ROW * 2 + (VEC ? STEPS * ROW : STEPS);
         const int ts = t0 + c * STEPS, ns = min(STEPS, t1 - ts);
+#pragma unroll 4
         for (int s = 0; s < ns; ++s) {
-            const float v = vs[s * cols + warp * REC_COLS + col8];
-            const float* qrow = buf + s * ROW + part * (KPT + 4);
-            const float* krow = buf + STEPS * ROW + s * ROW + part * (KPT + 4);
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            if (!VEC) {
-                const float a = buf[2 * STEPS * ROW + s];
+            const float2 v = *reinterpret_cast<const float2*>(vs + s * cols + warp * REC_COLS + 2 * pair);
+            const float* qrow = buf + s * ROW + part * RUN;
+            const float* krow = buf + STEPS * ROW + s * ROW + part * RUN;
+            const float* arow = buf + 2 * STEPS * ROW + (VEC ? s * ROW + part * RUN : s);
+            float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+            const float a = VEC ? 0.f : arow[0];
 #pragma unroll
-                for (int i = 0; i < KPT; i += 4) {
-                    const float4 k4 = *reinterpret_cast<const float4*>(krow + i);
-                    const float4 q4 = *reinterpret_cast<const float4*>(qrow + i);
-                    S[i] = fmaf(a, S[i], k4.x * v);         acc[0] = fmaf(S[i], q4.x, acc[0]);
-                    S[i + 1] = fmaf(a, S[i + 1], k4.y * v); acc[1] = fmaf(S[i + 1], q4.y, acc[1]);
-                    S[i + 2] = fmaf(a, S[i + 2], k4.z * v); acc[2] = fmaf(S[i + 2], q4.z, acc[2]);
-                    S[i + 3] = fmaf(a, S[i + 3], k4.w * v); acc[3] = fmaf(S[i + 3], q4.w, acc[3]);
-                }
-            } else {
-                const float* arow = buf + 2 * STEPS * ROW + s * ROW + part * (KPT + 4);
-#pragma unroll
-                for (int i = 0; i < KPT; i += 4) {
-                    const float4 a4 = *reinterpret_cast<const float4*>(arow + i);
-                    const float4 k4 = *reinterpret_cast<const float4*>(krow + i);
-                    const float4 q4 = *reinterpret_cast<const float4*>(qrow + i);
-                    S[i] = fmaf(a4.x, S[i], k4.x * v);         acc[0] = fmaf(S[i], q4.x, acc[0]);
-                    S[i + 1] = fmaf(a4.y, S[i + 1], k4.y * v); acc[1] = fmaf(S[i + 1], q4.y, acc[1]);
-                    S[i + 2] = fmaf(a4.z, S[i + 2], k4.z * v); acc[2] = fmaf(S[i + 2], q4.z, acc[2]);
-                    S[i + 3] = fmaf(a4.w, S[i + 3], k4.w * v); acc[3] = fmaf(S[i + 3], q4.w, acc[3]);
-                }
+            for (int i = 0; i < KPT; i += 4) {
+                const float4 a4 = VEC ? *reinterpret_cast<const float4*>(arow + i) : make_float4(a, a, a, a);
+                const float4 k4 = *reinterpret_cast<const float4*>(krow + i);
+                const float4 q4 = *reinterpret_cast<const float4*>(qrow + i);
+                S[i] = fmaf(a4.x, S[i], k4.x * v.x);           acc[0] = fmaf(S[i], q4.x, acc[0]);
+                S[i + 1] = fmaf(a4.y, S[i + 1], k4.y * v.x);   acc[1] = fmaf(S[i + 1], q4.y, acc[1]);
+                S[i + 2] = fmaf(a4.z, S[i + 2], k4.z * v.x);   acc[2] = fmaf(S[i + 2], q4.z, acc[2]);
+                S[i + 3] = fmaf(a4.w, S[i + 3], k4.w * v.x);   acc[3] = fmaf(S[i + 3], q4.w, acc[3]);
+                S1[i] = fmaf(a4.x, S1[i], k4.x * v.y);         acc1[0] = fmaf(S1[i], q4.x, acc1[0]);
+                S1[i + 1] = fmaf(a4.y, S1[i + 1], k4.y * v.y); acc1[1] = fmaf(S1[i + 1], q4.y, acc1[1]);
+                S1[i + 2] = fmaf(a4.z, S1[i + 2], k4.z * v.y); acc1[2] = fmaf(S1[i + 2], q4.z, acc1[2]);
+                S1[i + 3] = fmaf(a4.w, S1[i + 3], k4.w * v.y); acc1[3] = fmaf(S1[i + 3], q4.w, acc1[3]);
             }
-            float o = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-            o += __shfl_xor_sync(0xffffffffu, o, 8);
-            o += __shfl_xor_sync(0xffffffffu, o, 16);
-            if (part == 0 && v_ok)
-                A.out[((size_t)(ts + s) * H + h) * V + vcol] = fmaf(skip, vs[STEPS * cols + s * cols + warp * REC_COLS + col8], o);
+            float o = (acc[0] + acc[1]) + (acc[2] + acc[3]), o1 = (acc1[0] + acc1[1]) + (acc1[2] + acc1[3]);
+            o += __shfl_xor_sync(0xffffffffu, o, 1);   o1 += __shfl_xor_sync(0xffffffffu, o1, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);   o1 += __shfl_xor_sync(0xffffffffu, o1, 2);
+            o += __shfl_xor_sync(0xffffffffu, o, 4);   o1 += __shfl_xor_sync(0xffffffffu, o1, 4);
+            const float2 raw = *reinterpret_cast<const float2*>(vs + STEPS * cols + s * cols + warp * REC_COLS + 2 * pair);
+            // (stored as what it is, a store to global memory: through a generic pointer the compiler would have to assume
+            // that it may change the rows in shared memory, and could not start the next token's reads before it)
+            float* dst = A.out + ((size_t)(ts + s) * H + h) * V + vcol;
+            if (part == 0 && v_ok) st_global(dst, fmaf(skip, raw.x, o));
+            if (part == 1 && v_ok1) st_global(dst + 1, fmaf(skip, raw.y, o1));
         }
         if (more) settle(c + 1);          // (the other buffer: nobody reads it before the next barrier)
         __syncthreads();
@@ -352,7 +360,8 @@ __global__ void __launch_bounds__(256) recurrence_scan_kernel(const ScanArgs A) 
 #pragma unroll
     for (int i = 0; i < KPT; ++i) {
         const int k = part * KPT + i;
-        if (v_ok && k < K) sbase[(size_t)k * V + vcol] = S[i];
+        if (v_ok && k < K) sbase[(size_t)vcol * K + k] = S[i];
+        if (v_ok1 && k < K) sbase[(size_t)(vcol + 1) * K + k] = S1[i];
     }
 }
 
@@ -400,8 +409,8 @@ __global__ void sigmoid_gate_kernel(const T* o, int o_head, const T* __restrict_
     out[idx] = from_float<T>(v * sigmoidf_(to_float(gate[t * ld_gate + r])));
 }
 
-static int rec_kpt(int K) { return K <= 32 ? 8 : (K <= 64 ? 16 : (K <= 128 ? 32 : 64)); }
-static int rec_steps(int kpt) { return kpt <= 16 ? 16 : (kpt == 32 ? 8 : 4); }
+static int rec_kpt(int K) { return K <= 32 ? 4 : (K <= 64 ? 8 : (K <= 128 ? 16 : 32)); }
+static int rec_steps(int kpt) { return kpt == 4 ? 16 : (kpt <= 16 ? 8 : 4); }
 
 template <typename T, bool VEC>
 int launch_scan(const ScanArgs& a, int n_seqs, int warps, cudaStream_t s) {
@@ -413,10 +422,10 @@ int launch_scan(const ScanArgs& a, int n_seqs, int warps, cudaStream_t s) {
     const int row = rec_row(kpt);
     const size_t smem = 2 * (size_t)(args.steps * row * 2 + (VEC ? args.steps * row : args.steps) + 2 * args.steps * cols) * sizeof(float);
     switch (kpt) {
+        case 4: RMX_CHECK_LAUNCHED(launch_dependent(recurrence_scan_kernel<T, 4, VEC>, grid, block, smem, s, args), "recurrence_scan"); break;
         case 8: RMX_CHECK_LAUNCHED(launch_dependent(recurrence_scan_kernel<T, 8, VEC>, grid, block, smem, s, args), "recurrence_scan"); break;
         case 16: RMX_CHECK_LAUNCHED(launch_dependent(recurrence_scan_kernel<T, 16, VEC>, grid, block, smem, s, args), "recurrence_scan"); break;
-        case 32: RMX_CHECK_LAUNCHED(launch_dependent(recurrence_scan_kernel<T, 32, VEC>, grid, block, smem, s, args), "recurrence_scan"); break;
-        default: RMX_CHECK_LAUNCHED(launch_dependent(recurrence_scan_kernel<T, 64, VEC>, grid, block, smem, s, args), "recurrence_scan"); break;
+        default: RMX_CHECK_LAUNCHED(launch_dependent(recurrence_scan_kernel<T, 32, VEC>, grid, block, smem, s, args), "recurrence_scan"); break;
     }
     return 0;
 }
@@ -485,28 +494,27 @@ RMX_API int rmx_linear_recurrence(int mode, float* state, float* out, const int*
     a.heads = heads; a.K = K; a.V = V; a.steps = 0;
     if (mode == 0) {
         RMX_REQUIRE(groups > 0 && heads % groups == 0 && s1, "linear_recurrence: %d heads in %d groups", heads, groups);
-        const size_t total = (size_t)n_tokens * groups * row;
-        const dim3 grid((unsigned)((total + threads - 1) / threads));
+        const dim3 grid(n_tokens, (groups * row + threads - 1) / threads);
         if (dtype == RMX_F32)
             RMX_CHECK_LAUNCHED(launch_dependent(recurrence_prepare_ssd_kernel<float>, grid, dim3(threads), 0, s, (const float*)a0, ld0, (const float*)a1,
-                                                ld1, p0, p1, kf, qf, s0, s1, heads, groups, K, V, kpt, total), "recurrence_prepare");
+                                                ld1, p0, p1, kf, qf, s0, s1, heads, groups, K, V, kpt), "recurrence_prepare");
         else
             RMX_CHECK_LAUNCHED(launch_dependent(recurrence_prepare_ssd_kernel<__nv_bfloat16>, grid, dim3(threads), 0, s, (const __nv_bfloat16*)a0, ld0,
-                                                (const __nv_bfloat16*)a1, ld1, p0, p1, kf, qf, s0, s1, heads, groups, K, V, kpt, total),
+                                                (const __nv_bfloat16*)a1, ld1, p0, p1, kf, qf, s0, s1, heads, groups, K, V, kpt),
                                "recurrence_prepare");
         a.af = s1; a.v = a0; a.ld_v = ld0; a.v_scale = s0; a.skip = p2; a.row_heads = groups;
         return dtype == RMX_F32 ? launch_scan<float, false>(a, n_seqs, warps, s) : launch_scan<__nv_bfloat16, false>(a, n_seqs, warps, s);
     }
     RMX_REQUIRE(mode == 1, "linear_recurrence: unknown mode %d", mode);
     RMX_REQUIRE(a2 != nullptr, "linear_recurrence: the gated form needs values");
-    const size_t total = (size_t)n_tokens * heads * row;
-    const dim3 grid((unsigned)((total + threads - 1) / threads));
+    RMX_REQUIRE((heads * row + threads - 1) / threads <= 65535, "linear_recurrence: too many heads");
+    const dim3 grid(n_tokens, (heads * row + threads - 1) / threads);
     if (dtype == RMX_F32)
         RMX_CHECK_LAUNCHED(launch_dependent(recurrence_prepare_gate_kernel<float>, grid, dim3(threads), 0, s, (const float*)a0, ld0, (const float*)a1,
-                                            ld1, p0, p1, s0, kf, qf, heads, K, kpt, total), "recurrence_prepare");
+                                            ld1, p0, p1, s0, kf, qf, heads, K, kpt), "recurrence_prepare");
     else
         RMX_CHECK_LAUNCHED(launch_dependent(recurrence_prepare_gate_kernel<__nv_bfloat16>, grid, dim3(threads), 0, s, (const __nv_bfloat16*)a0, ld0,
-                                            (const __nv_bfloat16*)a1, ld1, p0, p1, s0, kf, qf, heads, K, kpt, total), "recurrence_prepare");
+                                            (const __nv_bfloat16*)a1, ld1, p0, p1, s0, kf, qf, heads, K, kpt), "recurrence_prepare");
     a.af = s0; a.v = a2; a.ld_v = ld2; a.v_scale = nullptr; a.skip = nullptr; a.row_heads = heads;
     return dtype == RMX_F32 ? launch_scan<float, true>(a, n_seqs, warps, s) : launch_scan<__nv_bfloat16, true>(a, n_seqs, warps, s);
 }

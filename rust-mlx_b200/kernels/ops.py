@@ -360,14 +360,15 @@ def sigmoid_gate(o, o_head, gate, out, heads, vdim):
 
 
 def short_conv(x, weight, bias, out, ring, batch, slots, activation=None, residual=False):
-    """A causal convolution over time on each channel: out_t = act(bias + sum_j weight[:, j] * x_(t - taps + 1 + j)) (+ x_t).
-    ``x`` and ``out``: [tokens, channels] (columns of wider rows allowed), ``weight`` float32 [channels, taps], ``ring``
+    """A causal convolution over time on each channel: out_t = act(bias + sum_j weight[j] * x_(t - taps + 1 + j)) (+ x_t).
+    ``x`` and ``out``: [tokens, channels] (columns of wider rows allowed), ``weight`` float32 [taps, channels] (taps-major:
+    the transpose of how checkpoints store it; its last row is the current token's), ``ring``
     [slots, max(taps - 1, 1), channels] of x's dtype: every sequence's last taps - 1 inputs, read for what lies before the
     step's tokens and written with the step's last ones."""
     lib = kernels_library()
     n, channels = x.shape
-    taps = weight.shape[1]
-    if weight.shape != (channels, taps) or out.shape != (n, channels) or x.stride(1) != 1 or out.stride(1) != 1 or out.dtype != x.dtype \
+    taps = weight.shape[0]
+    if weight.shape != (taps, channels) or out.shape != (n, channels) or x.stride(1) != 1 or out.stride(1) != 1 or out.dtype != x.dtype \
             or ring.dtype != x.dtype or ring.shape[1:] != (max(taps - 1, 1), channels):
         raise KernelError("short_conv: shapes or dtypes do not fit")
     if activation not in (None, "silu"):
@@ -383,8 +384,9 @@ def short_conv(x, weight, bias, out, ring, batch, slots, activation=None, residu
 
 
 def _recurrence_warps(batch, heads, vdim):
-    """Warps a block of the recurrence (8 columns of a head's state each): as many as cover a head's columns while the grid
-    still has a block or two an SM; fewer, so that more blocks run side by side, when few sequences step."""
+    """Warps a block of the recurrence (8 columns of a head's state each; a block's warps share the rows it fetches): as many
+    as cover a head's columns while the grid still has two blocks an SM; fewer, so that more blocks run side by side, when
+    few sequences step."""
     warps = max(1, min(8, -(-vdim // 8)))
     while warps > 1 and batch.n_seqs * heads * -(-vdim // (8 * warps)) < 2 * _sm_count():
         warps //= 2
@@ -411,13 +413,13 @@ def _recurrence_scratch(workspace, n, row_heads, heads, k, vector_decay):
     return kf, qf, ws.get("recurrence_step", (n, heads), torch.float32), ws.get("recurrence_decay", (n, heads), torch.float32)
 
 
-def recurrence_ssd(conv, dt, dt_bias, a_log, d_skip, state, out, batch, slots, heads, groups, k, v, workspace=None):
+def recurrence_ssd(conv, dt, dt_bias, a_log, d_skip, state, out, batch, slots, heads, groups, k, v, workspace=None, warps=None):
     """Per head S_t = exp(-exp(A_log) dt_t) S_(t-1) + dt_t B_t x_t^T, y_t = S_t^T C_t + D x_t, dt = softplus(raw + bias):
     ``conv`` rows [x (heads * v) | B (groups * k) | C (groups * k)], ``dt`` [tokens, heads] raw, ``state`` float32
-    [slots, heads, k, v] (read and written), ``out`` float32 [tokens, heads * v]."""
+    [slots, heads, v, k] (read and written; kept transposed), ``out`` float32 [tokens, heads * v]."""
     lib = kernels_library()
     n = conv.shape[0]
-    if conv.shape[1] != heads * v + 2 * groups * k or dt.shape != (n, heads) or out.shape != (n, heads * v) or state.shape[1:] != (heads, k, v) \
+    if conv.shape[1] != heads * v + 2 * groups * k or dt.shape != (n, heads) or out.shape != (n, heads * v) or state.shape[1:] != (heads, v, k) \
             or dt.dtype != conv.dtype:
         raise KernelError("recurrence_ssd: shapes do not fit")
     kf, qf, s0, s1 = _recurrence_scratch(workspace, n, groups, heads, k, False)
@@ -428,18 +430,18 @@ def recurrence_ssd(conv, dt, dt_bias, a_log, d_skip, state, out, batch, slots, h
                                     c_int(n), c_int(heads), c_int(k), c_int(v), p0, l0, p1, l1, c_void_p(0), c_int(0),
                                     _ptr(dt_bias, torch.float32, "dt_bias"), _ptr(a_log, torch.float32, "A_log"),
                                     _ptr(d_skip, torch.float32, "D"), c_int(groups), _ptr(kf), _ptr(qf), _ptr(s0), _ptr(s1),
-                                    c_int(_recurrence_warps(batch, heads, v)), c_int(dtype_code(conv)), _stream()))
+                                    c_int(warps or _recurrence_warps(batch, heads, v)), c_int(dtype_code(conv)), _stream()))
     _launched(2)
 
 
-def recurrence_gate(q, f, v, f_bias, lower, state, out, batch, slots, heads, k, vdim, workspace=None):
+def recurrence_gate(q, f, v, f_bias, lower, state, out, batch, slots, heads, k, vdim, workspace=None, warps=None):
     """Per head S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T silu(q_t), f = lower + (1 - lower) sigmoid(raw + bias):
     ``q`` and ``f`` [tokens, heads * k] raw projections, ``v`` [tokens, heads * vdim] (columns of wider rows allowed),
-    ``state`` float32 [slots, heads, k, vdim], ``out`` float32 [tokens, heads * vdim]."""
+    ``state`` float32 [slots, heads, vdim, k] (transposed), ``out`` float32 [tokens, heads * vdim]."""
     lib = kernels_library()
     n = q.shape[0]
     if q.shape != (n, heads * k) or f.shape != (n, heads * k) or v.shape != (n, heads * vdim) or out.shape != (n, heads * vdim) \
-            or state.shape[1:] != (heads, k, vdim) or f.dtype != q.dtype or v.dtype != q.dtype:
+            or state.shape[1:] != (heads, vdim, k) or f.dtype != q.dtype or v.dtype != q.dtype:
         raise KernelError("recurrence_gate: shapes do not fit")
     kf, qf, s0, _ = _recurrence_scratch(workspace, n, heads, heads, k, True)
     p0, l0 = _cols(q, "q")
@@ -450,7 +452,7 @@ def recurrence_gate(q, f, v, f_bias, lower, state, out, batch, slots, heads, k, 
                                     c_int(n), c_int(heads), c_int(k), c_int(vdim), p0, l0, p1, l1, p2, l2,
                                     _ptr(f_bias, torch.float32, "f_bias"), _ptr(lower, torch.float32, "lower"), c_void_p(0), c_int(1),
                                     _ptr(kf), _ptr(qf), _ptr(s0), c_void_p(0),
-                                    c_int(_recurrence_warps(batch, heads, vdim)), c_int(dtype_code(q)), _stream()))
+                                    c_int(warps or _recurrence_warps(batch, heads, vdim)), c_int(dtype_code(q)), _stream()))
     _launched(2)
 
 

@@ -1,7 +1,7 @@
 """A short causal convolution over time on each channel, with the last taps - 1 inputs of every request as its state.
 
 out_t = act(bias + sum_j w[:, j] * x_(t - taps + 1 + j)) (+ x_t with ``residual``); inputs before a sequence's first
-token are zero.  The weight is [channels, taps] (its last column is the current token's), held in float32; sums are
+token are zero.  The weight is [channels, taps] in a checkpoint (its last column is the current token's), held transposed in float32; sums are
 formed in float and rounded once.  The state is a ring [taps - 1, channels] in the compute dtype, input p at row
 p % (taps - 1), so a step reads what lies before its tokens and stores its last ones without moving anything.
 """
@@ -35,7 +35,7 @@ class ShortConv(Part):
 
     def bind(self, tensors, ctx):
         super().bind(tensors, ctx)
-        self.weight = tensors[self.name].contiguous()
+        self.weight = tensors[self.name].t().contiguous()      # taps-major, as the kernel reads it
         self.bias = tensors[self.bias_name].contiguous() if self.bias_name else None
 
     def forward(self, x, batch, cache, out):

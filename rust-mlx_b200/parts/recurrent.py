@@ -1,5 +1,5 @@
 """Mixers whose memory is a matrix a head that is stepped from token to token:  S_t = diag(a_t) S_(t-1) + k_t v_t^T,
-o_t = S_t^T q_t, with S (K x V, float32) in a state slot of the request.
+o_t = S_t^T q_t, with S (K x V, float32, kept transposed) in a state slot of the request.
 
 ``StateSpaceMixer`` (the state-space-duality layer, "Mamba-2"): one input product laid out [z | x | B | C | dt]; x, B and
 C pass a short causal convolution and silu; per head a = exp(-exp(A_log) dt) with dt = softplus(dt + dt_bias), k = dt B,
@@ -42,7 +42,7 @@ class StateSpaceMixer(Mixer):
         return [self.conv]
 
     def cache_specs(self):
-        return self.conv.cache_specs() + [CacheSpec("state", state_shape=(self.heads, self.state, self.vdim), state_dtype="float32")]
+        return self.conv.cache_specs() + [CacheSpec("state", state_shape=(self.heads, self.vdim, self.state), state_dtype="float32")]
 
     def param_specs(self):
         n = self.names
@@ -102,7 +102,7 @@ class GatedLinearMixer(Mixer):
         self.out_name = out_name
 
     def cache_spec(self):
-        return CacheSpec("state", state_shape=(self.heads, self.dim, self.vdim), state_dtype="float32")
+        return CacheSpec("state", state_shape=(self.heads, self.vdim, self.dim), state_dtype="float32")
 
     def param_specs(self):
         n, hk, hv = self.names, self.heads * self.dim, self.heads * self.vdim

@@ -48,7 +48,7 @@ def test_tensor_names_shapes_and_caches():
     kinds = [specs[i].kind for i in sorted(specs)]
     # every layer: the input convolution's ring, then what its mixer keeps
     assert kinds == ["state", "state", "state"] + ["state", "paged", "state"] + ["state", "state", "state"] + ["state", "paged", "state"]
-    assert specs[4].head_dim == 16 and specs[10].head_dim == 24 and specs[2].state_shape == (4, 16, 8)
+    assert specs[4].head_dim == 16 and specs[10].head_dim == 24 and specs[2].state_shape == (4, 8, 16)
 
 
 def test_plain_pieces_on_hand_made_numbers():

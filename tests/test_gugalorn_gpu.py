@@ -81,7 +81,7 @@ def test_short_convolution_in_portions_through_its_ring(dtype, taps, channels, a
         wide = torch.full((xin.shape[0], channels + extra), float("nan"), dtype=dt, device=DEV)
         wide[:, lead:lead + channels] = xin
         out = torch.empty_like(xin)
-        ops().short_conv(wide[:, lead:lead + channels], w.to(DEV), b.to(DEV) if bias else None, out, ring, batch,
+        ops().short_conv(wide[:, lead:lead + channels], w.t().contiguous().to(DEV), b.to(DEV) if bias else None, out, ring, batch,
                          slots[[s for s, _, _ in rows]].contiguous(), act, residual)
         at = 0
         for s, a, n in rows:
@@ -115,7 +115,7 @@ def test_state_space_recurrence_in_portions(dtype, heads, groups, k, v):
             S = decay[i][:, None, None] * S + step[i][:, None, None] * B[i][:, :, None] * xs[i][:, None, :]
             y[i] = torch.einsum("hkv,hk->hv", S, C[i]) + skip.double()[:, None] * xs[i]
         want.append(y.reshape(n, heads * v))
-    state = torch.full((6, heads, k, v), float("nan"), dtype=torch.float32, device=DEV)
+    state = torch.full((6, heads, v, k), float("nan"), dtype=torch.float32, device=DEV)
     slots = torch.tensor([5, 1, 2], dtype=torch.int32, device=DEV)
     state[[5, 1, 2]] = 0
     got = [torch.zeros(n, heads * v) for n in lengths]
@@ -155,7 +155,7 @@ def test_gated_linear_recurrence_in_portions(dtype, heads, k, v):
             S = gate[i][:, :, None] * S + (1 - gate[i])[:, :, None] * vv[i][:, None, :]
             o[i] = torch.einsum("hkv,hk->hv", S, qq[i])
         want.append(o.reshape(n, heads * v))
-    state = torch.zeros((4, heads, k, v), dtype=torch.float32, device=DEV)
+    state = torch.zeros((4, heads, v, k), dtype=torch.float32, device=DEV)
     slots = torch.tensor([2, 0, 3], dtype=torch.int32, device=DEV)
     got = [torch.zeros(n, heads * v) for n in lengths]
     for batch, rows in Steps(cuts):
