@@ -257,11 +257,24 @@ __global__ void __launch_bounds__(256) recurrence_scan_kernel(const ScanArgs A) 
     const T* vsrc = (const T*)A.v;
 
     float S[KPT], S1[KPT];
+    const bool vec4 = (K & 3) == 0;     // a lane's run of a column starts on a 16-byte boundary: four numbers a load
+    if (vec4) {
 #pragma unroll
-    for (int i = 0; i < KPT; ++i) {
-        const int k = part * KPT + i;
-        S[i] = (v_ok && k < K) ? sbase[(size_t)vcol * K + k] : 0.f;
-        S1[i] = (v_ok1 && k < K) ? sbase[(size_t)(vcol + 1) * K + k] : 0.f;
+        for (int i = 0; i < KPT; i += 4) {
+            const int k = part * KPT + i;
+            const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4 s0 = (v_ok && k < K) ? __ldcs(reinterpret_cast<const float4*>(sbase + (size_t)vcol * K + k)) : z;
+            const float4 s1 = (v_ok1 && k < K) ? __ldcs(reinterpret_cast<const float4*>(sbase + (size_t)(vcol + 1) * K + k)) : z;
+            S[i] = s0.x; S[i + 1] = s0.y; S[i + 2] = s0.z; S[i + 3] = s0.w;
+            S1[i] = s1.x; S1[i + 1] = s1.y; S1[i + 2] = s1.z; S1[i + 3] = s1.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < KPT; ++i) {
+            const int k = part * KPT + i;
+            S[i] = (v_ok && k < K) ? sbase[(size_t)vcol * K + k] : 0.f;
+            S1[i] = (v_ok1 && k < K) ? sbase[(size_t)(vcol + 1) * K + k] : 0.f;
+        }
     }
     const float skip = A.skip ? A.skip[h] : 0.f;
     const int n_chunks = (t1 - t0 + STEPS - 1) / STEPS;
@@ -356,6 +369,15 @@ __global__ void __launch_bounds__(256) recurrence_scan_kernel(const ScanArgs A) 
         }
         if (more) settle(c + 1);          // (the other buffer: nobody reads it before the next barrier)
         __syncthreads();
+    }
+    if (vec4) {
+#pragma unroll
+        for (int i = 0; i < KPT; i += 4) {
+            const int k = part * KPT + i;
+            if (v_ok && k < K) *reinterpret_cast<float4*>(sbase + (size_t)vcol * K + k) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+            if (v_ok1 && k < K) *reinterpret_cast<float4*>(sbase + (size_t)(vcol + 1) * K + k) = make_float4(S1[i], S1[i + 1], S1[i + 2], S1[i + 3]);
+        }
+        return;
     }
 #pragma unroll
     for (int i = 0; i < KPT; ++i) {

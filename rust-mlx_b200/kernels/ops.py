@@ -387,7 +387,7 @@ def _recurrence_warps(batch, heads, vdim):
     """Warps a block of the recurrence (8 columns of a head's state each; a block's warps share the rows it fetches): as many
     as cover a head's columns while the grid still has two blocks an SM; fewer, so that more blocks run side by side, when
     few sequences step."""
-    warps = max(1, min(8, -(-vdim // 8)))
+    warps = max(1, min(4, -(-vdim // 8)))      # (measured: 2 to 4 warps a block move a decode step's states fastest, 8 are slower)
     while warps > 1 and batch.n_seqs * heads * -(-vdim // (8 * warps)) < 2 * _sm_count():
         warps //= 2
     return warps
