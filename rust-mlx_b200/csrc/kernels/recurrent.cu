@@ -414,6 +414,47 @@ __global__ void group_rmsnorm_kernel(const float* __restrict__ y, const T* __res
     }
 }
 
+// The same with a warp a (token, group) and four numbers a lane and pass (the group's size, the row strides and the
+// weight's period are multiples of four): no barrier, 16-byte reads of y.  The order of a group's sum follows its size alone.
+template <typename T>
+__global__ void __launch_bounds__(128) group_rmsnorm4_kernel(const float* __restrict__ y, const T* __restrict__ gate, int ld_gate,
+                                                             const float* __restrict__ w, int period, float eps, T* __restrict__ out,
+                                                             int ld_out, int groups, int size, float out_scale, int total) {
+    allow_dependents();
+    wait_for_prior_kernels();
+    const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (item >= total) return;
+    const int t = item / groups, g = item - t * groups;
+    const float* row = y + ((size_t)t * groups + g) * size;
+    const T* grow = gate ? gate + (size_t)t * ld_gate + (size_t)g * size : nullptr;
+    T* orow = out + (size_t)t * ld_out + (size_t)g * size;
+    float ss = 0.f;
+    for (int i = lane * 4; i < size; i += 128) {
+        float4 u = *reinterpret_cast<const float4*>(row + i);
+        if (grow) {
+            u.x *= siluf_(to_float(grow[i])); u.y *= siluf_(to_float(grow[i + 1]));
+            u.z *= siluf_(to_float(grow[i + 2])); u.w *= siluf_(to_float(grow[i + 3]));
+        }
+        ss += u.x * u.x;
+        ss += u.y * u.y;
+        ss += u.z * u.z;
+        ss += u.w * u.w;
+    }
+    const float inv = rsqrtf(warp_sum(ss) / (float)size + eps) * out_scale;
+    for (int i = lane * 4; i < size; i += 128) {
+        float4 u = *reinterpret_cast<const float4*>(row + i);
+        if (grow) {
+            u.x *= siluf_(to_float(grow[i])); u.y *= siluf_(to_float(grow[i + 1]));
+            u.z *= siluf_(to_float(grow[i + 2])); u.w *= siluf_(to_float(grow[i + 3]));
+        }
+        const float4 wv = *reinterpret_cast<const float4*>(w + (g * size + i) % period);
+        orow[i] = from_float<T>(u.x * inv * wv.x);
+        orow[i + 1] = from_float<T>(u.y * inv * wv.y);
+        orow[i + 2] = from_float<T>(u.z * inv * wv.z);
+        orow[i + 3] = from_float<T>(u.w * inv * wv.w);
+    }
+}
+
 // out[t, h, 0:vdim] = o[t, h, 0:vdim] * sigmoid(gate[t, h * vdim + d]); o's heads are `o_head` numbers apart (heads
 // padded to a wider size keep their first vdim numbers), out is dense.  out may be o when o_head == vdim.
 template <typename T>
@@ -550,6 +591,22 @@ RMX_API int rmx_group_rmsnorm(const float* y, const void* gate, int ld_gate, con
     threads = threads > 256 ? 256 : threads;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid((unsigned)(n_tokens * groups));
+    // Which arrangement runs decides the order of a group's sum: in the 32-bit run the group's size alone may choose (the
+    // same bits however a step is cut); in bfloat16 a warp a group also serves long groups once there are many of them.
+    const bool many = dtype == RMX_BF16 && (long long)n_tokens * groups >= 1024;
+    if (size % 4 == 0 && period % 4 == 0 && ((uintptr_t)y & 15) == 0 && ((uintptr_t)w & 15) == 0 && (size <= 256 || (many && size <= 4096))) {
+        const int total = n_tokens * groups;
+        const dim3 grid4((unsigned)((total + 3) / 4));
+        if (dtype == RMX_F32)
+            RMX_CHECK_LAUNCHED(launch_dependent(group_rmsnorm4_kernel<float>, grid4, dim3(128), 0, s, y, (const float*)gate, ld_gate, w, period, eps,
+                                                (float*)out, ld_out, groups, size, out_scale, total), "group_rmsnorm");
+        else if (dtype == RMX_BF16)
+            RMX_CHECK_LAUNCHED(launch_dependent(group_rmsnorm4_kernel<__nv_bfloat16>, grid4, dim3(128), 0, s, y, (const __nv_bfloat16*)gate, ld_gate,
+                                                w, period, eps, (__nv_bfloat16*)out, ld_out, groups, size, out_scale, total), "group_rmsnorm");
+        else
+            RMX_FAIL("group_rmsnorm: unknown dtype %d", dtype);
+        return 0;
+    }
     if (dtype == RMX_F32)
         RMX_CHECK_LAUNCHED(launch_dependent(group_rmsnorm_kernel<float>, grid, dim3(threads), 0, s, y, (const float*)gate, ld_gate, w, period, eps,
                                             (float*)out, ld_out, groups, size, out_scale), "group_rmsnorm");
