@@ -283,7 +283,7 @@ __global__ void __launch_bounds__(WARPS * 32, 8) qk_rope_cache_128_wide_kernel(
 // hd >= max(dq, dv) numbers, the rest of a head is written as zeros (a zero in q and k adds nothing to a score, and the
 // zero columns of a value head come out as zeros).  Input rows are [q | k | v].  One block a token.
 template <typename T>
-__global__ void __launch_bounds__(256) qk_whole_norm_rope_cache_kernel(
+__global__ void __launch_bounds__(1024) qk_whole_norm_rope_cache_kernel(
     const T* __restrict__ qkv, int row_stride, const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
     const float* __restrict__ inv_freq, int rotary_dim, const float* __restrict__ cos_sin, const int* __restrict__ positions,
     const int* __restrict__ seq_index, const int* __restrict__ block_table, int table_stride, int page_size,
@@ -379,7 +379,9 @@ RMX_API int rmx_qk_whole_norm_rope_cache(const void* qkv, int row_stride, const 
             (float*)v_pool, (float*)q_out, nq, nkv, dq, dv, hd, write_kv, status), "qk_whole_norm_rope_cache");
     } else if (dtype == RMX_BF16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(qk_whole_norm_rope_cache_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        RMX_CHECK_LAUNCHED(launch_dependent(qk_whole_norm_rope_cache_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), smem, s,
+        // (few tokens, decoding: a block a token is all the parallelism there is, so the block is as large as it can be; the
+        // 32-bit run keeps one block size, because the size decides the order in which the squares are added)
+        RMX_CHECK_LAUNCHED(launch_dependent(qk_whole_norm_rope_cache_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(n_tokens <= 64 ? 1024 : 256), smem, s,
             (const __nv_bfloat16*)qkv, row_stride, q_norm, k_norm, eps, inv_freq, rotary_dim, cos_sin, positions, seq_index, block_table,
             table_stride, page_size, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, (__nv_bfloat16*)q_out, nq, nkv, dq, dv, hd, write_kv,
             status), "qk_whole_norm_rope_cache");

@@ -52,7 +52,7 @@ CONFIGS = {"G1": (G1, 16), "G2": (G2, 64), "G3": (G3, 16)}
 def make_folder(tmp_path, raw: dict, seed: int = 0, sharp: float = 8.0, out_boost: float = 12.0) -> str:
     """A model folder from the engine's random-weights mode, with the tensors whose useful range is not N(0, 0.02) drawn
     anew: lower bounds of the forget gate in (0.05, 0.95), its bias N(0, 1), A_log in (-1.5, 0.5), dt_bias in (-3, 0.5),
-    D around 1, convolution taps of some size; the q and k projections times ``sharp`` and their norm weights spread (a
+    D near 1, convolution taps of some size; the q and k projections times ``sharp`` and their norm weights spread (a
     few keys carry most of a row's weight, so a lost or stale key shows); output projections times ``out_boost`` (what a
     mixer adds to the stream is comparable to the stream)."""
     from safetensors.torch import load_file, save_file
