@@ -231,19 +231,6 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-// Two floats in one 64-bit register and the multiply-add that works on such pairs: each half is an ordinary fused
-// multiply-add, so the numbers are those of two scalar operations, in half the instructions.
-__device__ __forceinline__ uint64_t pair2(float a, float b) {
-    uint64_t r;
-    asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(a), "f"(b));
-    return r;
-}
-__device__ __forceinline__ void unpair2(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;\n" : "=f"(a), "=f"(b) : "l"(v)); }
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-    uint64_t r;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-    return r;
-}
 __device__ __forceinline__ void st_global(float* p, float v) { asm volatile("st.global.f32 [%0], %1;\n" ::"l"(p), "f"(v)); }
 template <int N> __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
@@ -269,8 +256,7 @@ __global__ void __launch_bounds__(256) recurrence_scan_kernel(const ScanArgs A) 
     float* sbase = A.state + ((size_t)A.slots[seq] * H + h) * K * V;
     const T* vsrc = (const T*)A.v;
 
-    // the lane's numbers of its two columns, neighbours in K paired
-    uint64_t S[KPT / 2], S1[KPT / 2];
+    float S[KPT], S1[KPT];
     const bool vec4 = (K & 3) == 0;     // a lane's run of a column starts on a 16-byte boundary: four numbers a load
     if (vec4) {
 #pragma unroll
@@ -279,16 +265,15 @@ __global__ void __launch_bounds__(256) recurrence_scan_kernel(const ScanArgs A) 
             const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
             const float4 s0 = (v_ok && k < K) ? __ldcs(reinterpret_cast<const float4*>(sbase + (size_t)vcol * K + k)) : z;
             const float4 s1 = (v_ok1 && k < K) ? __ldcs(reinterpret_cast<const float4*>(sbase + (size_t)(vcol + 1) * K + k)) : z;
-            S[i / 2] = pair2(s0.x, s0.y); S[i / 2 + 1] = pair2(s0.z, s0.w);
-            S1[i / 2] = pair2(s1.x, s1.y); S1[i / 2 + 1] = pair2(s1.z, s1.w);
+            S[i] = s0.x; S[i + 1] = s0.y; S[i + 2] = s0.z; S[i + 3] = s0.w;
+            S1[i] = s1.x; S1[i + 1] = s1.y; S1[i + 2] = s1.z; S1[i + 3] = s1.w;
         }
     } else {
 #pragma unroll
-        for (int i = 0; i < KPT; i += 2) {
+        for (int i = 0; i < KPT; ++i) {
             const int k = part * KPT + i;
-            S[i / 2] = pair2((v_ok && k < K) ? sbase[(size_t)vcol * K + k] : 0.f, (v_ok && k + 1 < K) ? sbase[(size_t)vcol * K + k + 1] : 0.f);
-            S1[i / 2] = pair2((v_ok1 && k < K) ? sbase[(size_t)(vcol + 1) * K + k] : 0.f,
-                              (v_ok1 && k + 1 < K) ? sbase[(size_t)(vcol + 1) * K + k + 1] : 0.f);
+            S[i] = (v_ok && k < K) ? sbase[(size_t)vcol * K + k] : 0.f;
+            S1[i] = (v_ok1 && k < K) ? sbase[(size_t)(vcol + 1) * K + k] : 0.f;
         }
     }
     const float skip = A.skip ? A.skip[h] : 0.f;
@@ -355,25 +340,23 @@ __global__ void __launch_bounds__(256) recurrence_scan_kernel(const ScanArgs A) 
             const float* qrow = buf + s * ROW + part * RUN;
             const float* krow = buf + STEPS * ROW + s * ROW + part * RUN;
             const float* arow = buf + 2 * STEPS * ROW + (VEC ? s * ROW + part * RUN : s);
-            uint64_t acc[2] = {0ull, 0ull}, acc1[2] = {0ull, 0ull};      // (the bits of 0.f twice)
-            const uint64_t vv = pair2(v.x, v.x), vv1 = pair2(v.y, v.y);
+            float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
             const float a = VEC ? 0.f : arow[0];
-            const uint64_t aa = pair2(a, a);
 #pragma unroll
             for (int i = 0; i < KPT; i += 4) {
-                const ulonglong2 a2 = VEC ? *reinterpret_cast<const ulonglong2*>(arow + i) : make_ulonglong2(aa, aa);
-                const ulonglong2 k2 = *reinterpret_cast<const ulonglong2*>(krow + i);
-                const ulonglong2 q2 = *reinterpret_cast<const ulonglong2*>(qrow + i);
-                // S = a S + k v, then the output's sum takes the new S; x * y + 0 is the rounded product
-                S[i / 2] = fma2(a2.x, S[i / 2], fma2(k2.x, vv, 0ull));             acc[0] = fma2(S[i / 2], q2.x, acc[0]);
-                S[i / 2 + 1] = fma2(a2.y, S[i / 2 + 1], fma2(k2.y, vv, 0ull));     acc[1] = fma2(S[i / 2 + 1], q2.y, acc[1]);
-                S1[i / 2] = fma2(a2.x, S1[i / 2], fma2(k2.x, vv1, 0ull));          acc1[0] = fma2(S1[i / 2], q2.x, acc1[0]);
-                S1[i / 2 + 1] = fma2(a2.y, S1[i / 2 + 1], fma2(k2.y, vv1, 0ull));  acc1[1] = fma2(S1[i / 2 + 1], q2.y, acc1[1]);
+                const float4 a4 = VEC ? *reinterpret_cast<const float4*>(arow + i) : make_float4(a, a, a, a);
+                const float4 k4 = *reinterpret_cast<const float4*>(krow + i);
+                const float4 q4 = *reinterpret_cast<const float4*>(qrow + i);
+                S[i] = fmaf(a4.x, S[i], k4.x * v.x);           acc[0] = fmaf(S[i], q4.x, acc[0]);
+                S[i + 1] = fmaf(a4.y, S[i + 1], k4.y * v.x);   acc[1] = fmaf(S[i + 1], q4.y, acc[1]);
+                S[i + 2] = fmaf(a4.z, S[i + 2], k4.z * v.x);   acc[2] = fmaf(S[i + 2], q4.z, acc[2]);
+                S[i + 3] = fmaf(a4.w, S[i + 3], k4.w * v.x);   acc[3] = fmaf(S[i + 3], q4.w, acc[3]);
+                S1[i] = fmaf(a4.x, S1[i], k4.x * v.y);         acc1[0] = fmaf(S1[i], q4.x, acc1[0]);
+                S1[i + 1] = fmaf(a4.y, S1[i + 1], k4.y * v.y); acc1[1] = fmaf(S1[i + 1], q4.y, acc1[1]);
+                S1[i + 2] = fmaf(a4.z, S1[i + 2], k4.z * v.y); acc1[2] = fmaf(S1[i + 2], q4.z, acc1[2]);
+                S1[i + 3] = fmaf(a4.w, S1[i + 3], k4.w * v.y); acc1[3] = fmaf(S1[i + 3], q4.w, acc1[3]);
             }
-            float c0, c1, c2, c3, d0, d1, d2, d3;
-            unpair2(acc[0], c0, c1); unpair2(acc[1], c2, c3);
-            unpair2(acc1[0], d0, d1); unpair2(acc1[1], d2, d3);
-            float o = (c0 + c1) + (c2 + c3), o1 = (d0 + d1) + (d2 + d3);
+            float o = (acc[0] + acc[1]) + (acc[2] + acc[3]), o1 = (acc1[0] + acc1[1]) + (acc1[2] + acc1[3]);
             o += __shfl_xor_sync(0xffffffffu, o, 1);   o1 += __shfl_xor_sync(0xffffffffu, o1, 1);
             o += __shfl_xor_sync(0xffffffffu, o, 2);   o1 += __shfl_xor_sync(0xffffffffu, o1, 2);
             o += __shfl_xor_sync(0xffffffffu, o, 4);   o1 += __shfl_xor_sync(0xffffffffu, o1, 4);
@@ -391,24 +374,16 @@ __global__ void __launch_bounds__(256) recurrence_scan_kernel(const ScanArgs A) 
 #pragma unroll
         for (int i = 0; i < KPT; i += 4) {
             const int k = part * KPT + i;
-            float4 s0, s1;
-            unpair2(S[i / 2], s0.x, s0.y); unpair2(S[i / 2 + 1], s0.z, s0.w);
-            unpair2(S1[i / 2], s1.x, s1.y); unpair2(S1[i / 2 + 1], s1.z, s1.w);
-            if (v_ok && k < K) *reinterpret_cast<float4*>(sbase + (size_t)vcol * K + k) = s0;
-            if (v_ok1 && k < K) *reinterpret_cast<float4*>(sbase + (size_t)(vcol + 1) * K + k) = s1;
+            if (v_ok && k < K) *reinterpret_cast<float4*>(sbase + (size_t)vcol * K + k) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+            if (v_ok1 && k < K) *reinterpret_cast<float4*>(sbase + (size_t)(vcol + 1) * K + k) = make_float4(S1[i], S1[i + 1], S1[i + 2], S1[i + 3]);
         }
         return;
     }
 #pragma unroll
-    for (int i = 0; i < KPT; i += 2) {
+    for (int i = 0; i < KPT; ++i) {
         const int k = part * KPT + i;
-        float x0, x1, y0, y1;
-        unpair2(S[i / 2], x0, x1);
-        unpair2(S1[i / 2], y0, y1);
-        if (v_ok && k < K) sbase[(size_t)vcol * K + k] = x0;
-        if (v_ok && k + 1 < K) sbase[(size_t)vcol * K + k + 1] = x1;
-        if (v_ok1 && k < K) sbase[(size_t)(vcol + 1) * K + k] = y0;
-        if (v_ok1 && k + 1 < K) sbase[(size_t)(vcol + 1) * K + k + 1] = y1;
+        if (v_ok && k < K) sbase[(size_t)vcol * K + k] = S[i];
+        if (v_ok1 && k < K) sbase[(size_t)(vcol + 1) * K + k] = S1[i];
     }
 }
 
