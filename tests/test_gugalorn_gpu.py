@@ -521,3 +521,47 @@ def test_trace_tool_runs_this_family(folders, tmp_path):
     got = replay.run_trace_tool(folders["G1"], "float32", steps, str(tmp_path / "out"), replay.tokens_needed(steps, 64), raw["vocab"])
     for rid, toks in reqs.items():
         assert tg.row_error(got[rid], plain_logits(folders["G1"], raw, toks)).max().item() < 2e-4
+
+
+def random_configuration(seed):
+    """Sizes, constants and the order of layers drawn from a seed (every choice a model of this family may make)."""
+    import random
+    r = random.Random(seed)
+    width = r.choice([48, 72, 96, 136])
+    layers = []
+    for _ in range(r.randint(2, 5)):
+        ff = r.choice([0, 0, 32, 80])
+        if r.random() < 0.5:
+            heads = r.choice([2, 3, 4, 6])
+            vdim = r.choice([4, 8, 12, 16])
+            groups = r.choice([g for g in (1, 2, 3, 6) if heads % g == 0])
+            norm_groups = r.choice([g for g in (1, 2, heads) if (heads * vdim) % g == 0])
+            layers.append(tg.ssm(heads, vdim, r.choice([8, 16, 24, 32, 48]), groups, r.choice([1, 2, 3, 4]), norm_groups, ff))
+        else:
+            kv = r.choice([1, 2, 3])
+            heads = kv * r.choice([1, 2, 3])
+            dim, vdim = r.choice([8, 16, 32, 64]), r.choice([8, 16, 32, 64])
+            dims = r.choice([0, dim // 2, dim]) // 2 * 2
+            left = (heads, kv, dim, vdim, dims, r.choice([50.0, 1e4, 1e6]), r.uniform(0.1, 0.3))
+            right = (r.choice([1, 2, 4, 6]), r.choice([4, 8, 12, 16, 48]), r.choice([8, 16, 64]))
+            layers.append(tg.par(left, right, round(r.uniform(0.5, 1.5), 3), round(r.uniform(0.5, 1.5), 3), ff))
+    return tg.model(r.randint(50, 300), width, r.choice([0, 2, 3, 4, 5]), layers, eps=r.choice([1e-5, 1e-6]), scale=r.choice([0.5, 1.0, 2.0]))
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_configurations_replayed_in_mixed_steps(tmp_path, seed):
+    from rust_mlx_b200.engine import Engine
+    raw = random_configuration(seed)
+    folder = tg.make_folder(tmp_path, raw, seed=100 + seed)
+    reqs = requests_for(raw, [70, 1, 33, 2, 90, 17], seed=seed)
+    want = {rid: plain.forward(raw, tg.weights(folder), toks) for rid, toks in reqs.items()}
+    page = [16, 32, 64][seed % 3]
+    for dtype, bound in (("float32", 2e-4), ("bfloat16", 0.15)):
+        for cut in (replay.mixed, replay.portions):
+            steps = cut(reqs)
+            eng = Engine(folder, dtype=dtype, max_tokens=replay.tokens_needed(steps, page), page_size=page, max_requests=4)
+            got = replay.run_engine(eng, steps)
+            eng.pools.table.check()
+            for rid in reqs:
+                err = tg.row_error(got[rid], want[rid])
+                assert err.max().item() < bound, (seed, dtype, rid, int(err.argmax()), err.max().item(), raw)
